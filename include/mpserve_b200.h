@@ -1,0 +1,153 @@
+/*
+ * mpserve_b200.h -- C ABI of libmpserve_b200.so
+ *
+ * B200 (sm_100a) implementation of one path of MPServe: reconstructing BF16 weights from an FP8
+ * (or AWQ-INT4) checkpoint plus its context-conditioned Huffman sidecar, and building that sidecar.
+ * Plain pointers and sizes only; every pointer marked "device" must be a CUDA device pointer on the
+ * current device.  All launches are asynchronous on `stream` (a cudaStream_t passed as void*).
+ *
+ * Return value of every int function: 0 on success, a negative MPS_ERR_* for bad arguments, or a
+ * positive cudaError_t value when a CUDA call failed (text via mps_last_error()).
+ *
+ * Each entry point names the reference interface it replaces (file:line in the reference tree).
+ */
+#ifndef MPSERVE_B200_H
+#define MPSERVE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define MPS_API __attribute__((visibility("default")))
+#else
+#define MPS_API
+#endif
+
+#define MPS_OK 0
+#define MPS_ERR_INVALID (-1)      /* bad argument (reference: std::invalid_argument -> ValueError) */
+#define MPS_ERR_UNSUPPORTED (-2)  /* valid but not implemented by this build                      */
+#define MPS_ERR_WORKSPACE (-3)    /* workspace missing or too small                                */
+
+/* Library / device ---------------------------------------------------------------------------- */
+
+/* Version of this ABI (bumped on incompatible change). */
+MPS_API int mps_abi_version(void);
+
+/* Text of the last error raised on the calling thread. */
+MPS_API const char* mps_last_error(void);
+
+/* Replaces MPServe_cuda.cuda_clock_rate_khz (kernel/wrapper.cpp:133-141): SM clock of the current
+ * device in kHz, or a negative/positive error code as above. */
+MPS_API int64_t mps_cuda_clock_rate_khz(void);
+
+/* Bytes of zero-initialised device scratch every decode call needs (work-queue counters).  The
+ * caller allocates it once per (device, stream), zero-fills it once, and passes it to every call;
+ * the kernels leave it zeroed again.  Two calls that may overlap on the GPU need two workspaces. */
+MPS_API size_t mps_workspace_bytes(void);
+
+/* One compressed tensor (all pointers device) ---------------------------------------------------
+ * mode 0: FP8 rectangular buckets, L=7, 256 contexts   (huffman_decode_fp8_entry)
+ * mode 1: AWQ-INT4 rectangular buckets, L=11, 16 ctx   (huffman_decode_awq_int4_bucket_entry)
+ * mode 2: AWQ-INT4 ragged buckets by exact scale       (huffman_decode_awq_int4_bucket_by_scale_entry)
+ */
+typedef struct mps_bucket_tensor {
+    const uint8_t* ctx_bytes;          /* [n*m] fp8 byte or unpacked int4 code per element        */
+    const uint64_t* bitstream;         /* [bitstream_words] MSB-first                             */
+    int64_t bitstream_words;
+    const uint16_t* decode_syms;       /* [num_tables, 2^L]                                       */
+    const uint8_t* decode_lens;        /* [num_tables, 2^(L-1)] two 4-bit entries per byte        */
+    int64_t num_tables;
+    const int32_t* bucket_table;       /* [num_buckets, 256 or 16] context -> table id or -1      */
+    const int32_t* bucket_col_start;   /* [num_buckets]            (modes 0,1)                    */
+    const int32_t* bucket_col_len;     /* [num_buckets]            (modes 0,1)                    */
+    const int32_t* bucket_row_offsets; /* [num_buckets+1] CSR      (modes 0,1; group offsets in 2) */
+    const int32_t* row_indices;        /* [num_rows]               (modes 0,1; group rows in 2)    */
+    const int32_t* group_col_start;    /* [num_rows]               (mode 2 only)                   */
+    int64_t num_rows;                  /* length of row_indices / group arrays                    */
+    const uint32_t* thread_startbit;   /* [num_buckets, k+1]                                      */
+    const int64_t* bucket_bit_base;    /* [num_buckets+1]                                         */
+    int64_t num_buckets;
+    int32_t k;                         /* sub-streams per bucket                                  */
+    int32_t group_size;                /* mode 2 only                                             */
+    int32_t mode;
+    int32_t reserved;
+    int64_t n, m;
+    uint16_t* out;                     /* [n*m] BF16 bit patterns                                 */
+} mps_bucket_tensor;
+
+/* Decode ---------------------------------------------------------------------------------------- */
+
+/* Replaces huffman_cpp::huffman_decode_fp8_entry (kernel/decode_huffman.cu:591-758; Python name
+ * huffman_decode_fp8, kernel/wrapper.cpp:457-503).  max_len must be 7.  Output is written to
+ * `out_bf16` (caller-allocated [n,m] BF16).  Unlike the shipped kernel, the ESC flag of a length
+ * nibble is honoured (16 raw bits follow the code, as the encoder writes them) and elements map to
+ * rows/columns by true division, so buckets narrower than k decode correctly. */
+MPS_API int mps_decode_fp8(const uint8_t* fp8_u8, const uint64_t* bitstream_u64, int64_t bitstream_words,
+                   const uint16_t* decode_syms_u16, const uint8_t* decode_lens_u8, int64_t num_tables,
+                   const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                   const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                   const int32_t* row_indices_i32, int64_t num_row_indices,
+                   const uint32_t* bucket_thread_startbit_u32, const int64_t* bucket_bit_base_i64,
+                   int64_t num_buckets, int32_t k, int64_t n, int64_t m, int64_t max_len,
+                   uint16_t* out_bf16, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces huffman_cpp::huffman_decode_awq_int4_bucket_entry (kernel/decode_huffman.cu:877-1017;
+ * Python name huffman_decode_awq_int4_bucket, kernel/wrapper.cpp:324-369).  max_len must be 11. */
+MPS_API int mps_decode_awq_int4_bucket(const uint8_t* int4_values_u8, const uint64_t* bitstream_u64, int64_t bitstream_words,
+                               const uint16_t* decode_syms_u16, const uint8_t* decode_lens_u8, int64_t num_tables,
+                               const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                               const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                               const int32_t* row_indices_i32, int64_t num_row_indices,
+                               const uint32_t* bucket_thread_startbit_u32, const int64_t* bucket_bit_base_i64,
+                               int64_t num_buckets, int32_t k, int64_t n, int64_t m, int64_t max_len,
+                               uint16_t* out_bf16, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces huffman_cpp::huffman_decode_awq_int4_bucket_by_scale_entry
+ * (kernel/decode_huffman.cu:760-875; Python name huffman_decode_awq_int4_bucket_by_scale,
+ * kernel/wrapper.cpp:371-416).  max_len must be 11. */
+MPS_API int mps_decode_awq_int4_bucket_by_scale(const uint8_t* int4_values_u8, const uint64_t* bitstream_u64,
+                                        int64_t bitstream_words, const uint16_t* decode_syms_u16,
+                                        const uint8_t* decode_lens_u8, int64_t num_tables,
+                                        const int32_t* bucket_table_i32, const int32_t* bucket_group_offsets_i32,
+                                        const int32_t* group_rows_i32, const int32_t* group_col_start_i32,
+                                        int64_t num_groups, const uint32_t* bucket_thread_startbit_u32,
+                                        const int64_t* bucket_bit_base_i64, int64_t num_buckets, int32_t k,
+                                        int64_t n, int64_t m, int64_t max_len, int64_t group_size,
+                                        uint16_t* out_bf16, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces huffman_decode_cpp::huffman_decode_awq_shared_table_entry
+ * (kernel/decode_huffman_encode_only.cu:279-383, 416-444; Python name
+ * huffman_decode_awq_shared_table, kernel/wrapper.cpp:212-255).  Output int16 [out_len].  Every
+ * stream is decoded (the shipped launch silently stops after 65535 streams). */
+MPS_API int mps_decode_awq_shared_table(const uint64_t* bitstream_u64, int64_t bitstream_words,
+                                const int16_t* decode_syms_i16, const uint8_t* decode_nbits_u8,
+                                int64_t num_streams, const int64_t* scale_bit_base_i64, int64_t num_scales_plus1,
+                                const uint32_t* chunk_startbit_rel_u32, const uint32_t* chunk_out_base_u32,
+                                const uint32_t* chunk_meta_u32, const int32_t* chunk_scale_id_i32, int64_t num_chunks,
+                                const int32_t* out_idx_i32, const int64_t* stream_chunk_ofs_i64,
+                                const int32_t* stream_chunk_ids_i32, int64_t out_len, int64_t max_len,
+                                int16_t* out_i16, void* stream);
+
+/* Many tensors in one launch (whole-model decompression).  `tensors_dev` is a DEVICE array of
+ * `count` descriptors; `item_prefix_dev` a DEVICE array of count+1 int64 work-item prefix sums as
+ * returned by mps_bucket_batch_plan for the same descriptors.  No reference counterpart: the
+ * reference launches one kernel per weight (scripts/mpserve_vllm_fp8_huffman.py:526-543). */
+MPS_API int mps_bucket_batch_plan(const mps_bucket_tensor* tensors_host, int count, int64_t* item_prefix_host,
+                          int32_t* threads_out, int32_t* chains_out);
+MPS_API int mps_decode_bucket_batch(const mps_bucket_tensor* tensors_dev, const int64_t* item_prefix_dev, int count,
+                            int64_t total_items, int32_t threads, int32_t chains, int32_t mode,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* Checksum of a decoded tensor: sum of the 16-bit patterns (mod 2^64) and an XOR fold of
+ * (pattern * (index+1)) -- what ranks all-reduce after a sharded decode.  result_dev: device
+ * uint64[2], accumulated into (zero it first). */
+MPS_API int mps_checksum_u16(const uint16_t* data_dev, int64_t count, uint64_t* result_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MPSERVE_B200_H */

@@ -1,0 +1,692 @@
+// Bucketed sub-stream Huffman decode for the FP8 (L=7, 256 contexts) and AWQ-INT4 (L=11, 16
+// contexts) sidecar formats, rectangular or ragged buckets, one tensor or a whole model per launch.
+//
+// Format recap (what the encoder guarantees, kernel/build_huffman.cu:811-918 in the reference):
+// bucket b owns rows x column-window (or a list of groups); its elements, flattened row-major to
+// e in [0,total), are dealt round-robin to k_eff = min(k, max(1,total)) sub-streams: sub-stream t
+// holds e = t, t+k_eff, ... as one contiguous run of prefix codes starting at bit
+// bucket_bit_base[b] + startbit[b][t].  The code of an element is chosen by its context byte (the
+// FP8 byte / INT4 code): gid = bucket_table[b][ctx] selects a 2^L-entry lookup table.
+//
+// Design for B200:
+//  * persistent CTAs (one per SM: the fused table takes 128 KB of shared memory) pull work items
+//    (tensor, bucket, chunk of sub-streams) from a global counter;
+//  * per item the bucket's tables are fused once into 32-bit entries sym | len<<16 | esc<<31 laid
+//    out [ctx][prefix], so a symbol costs ONE shared-memory load; staging is skipped when the next
+//    item uses the same tables;
+//  * each thread decodes CH adjacent sub-streams in lock-step: CH independent dependency chains for
+//    ILP, one CH-byte context load and one 2*CH-byte BF16 store per step (16 B stores at CH=8),
+//    both fully coalesced across the warp; context bytes are prefetched a block of steps ahead;
+//  * every sub-stream keeps a 64-bit left-aligned bit window in registers, refilled 32 bits at a
+//    time at a fixed cadence (every 32/L symbols) so that refills are warp-uniform, not divergent;
+//  * ESC (raw 16-bit symbol after the code) is rare: buckets whose tables contain no ESC entry run
+//    a loop with no ESC test at all; the others test per symbol.
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "mps_common.cuh"
+
+namespace mps {
+
+// ------------------------------------------------------------------------------------------------
+// error plumbing
+// ------------------------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("%s failed: %s", what, cudaGetErrorString(e));
+    return (int)e;
+}
+
+// ------------------------------------------------------------------------------------------------
+// kernel
+// ------------------------------------------------------------------------------------------------
+constexpr int kTableEntries = 32768;  // 256 ctx x 2^7 == 16 ctx x 2^11
+constexpr int kRowCap = 2048;         // rows / groups of a bucket cached in shared memory
+constexpr int kPrefixCap = 1024;      // tensors of a batch whose item prefix is cached in shared memory
+constexpr int kSteps = 4;             // steps per software-pipeline block
+
+struct BatchArgs {
+    mps_bucket_tensor single;            // used when tensors == nullptr
+    const mps_bucket_tensor* tensors;    // device array, or nullptr
+    const int64_t* item_prefix;          // device [count+1], or nullptr (single tensor)
+    int count;
+    int total_items;
+};
+
+struct Smem {
+    uint32_t tbl[kTableEntries];
+    long long rowbase[kRowCap];
+    int32_t gid[256];
+    long long prefix[kPrefixCap + 1];
+    int item;
+    int staged_tensor;
+};
+
+template <int CH> struct Ctx;
+template <> struct Ctx<1> {
+    using T = uint32_t;
+    static __device__ __forceinline__ T ld(const uint8_t* p) { return ld_stream_u8(p); }
+    static __device__ __forceinline__ uint32_t byte(T v, int) { return v; }
+};
+template <> struct Ctx<2> {
+    using T = uint32_t;
+    static __device__ __forceinline__ T ld(const uint8_t* p) { return ld_stream_u16(p); }
+    static __device__ __forceinline__ uint32_t byte(T v, int c) { return (v >> (8 * c)) & 0xFFu; }
+};
+template <> struct Ctx<4> {
+    using T = uint32_t;
+    static __device__ __forceinline__ T ld(const uint8_t* p) { return ld_stream_u32(p); }
+    static __device__ __forceinline__ uint32_t byte(T v, int c) { return (v >> (8 * c)) & 0xFFu; }
+};
+template <> struct Ctx<8> {
+    using T = uint2;
+    static __device__ __forceinline__ T ld(const uint8_t* p) { return ld_stream_u64(p); }
+    static __device__ __forceinline__ uint32_t byte(T v, int c) { return (((c < 4) ? v.x : v.y) >> (8 * (c & 3))) & 0xFFu; }
+};
+
+template <int CH>
+__device__ __forceinline__ void store_syms(uint16_t* p, const uint32_t (&e)[CH]) {
+    if constexpr (CH == 1) st_stream_u16(p, e[0]);
+    else if constexpr (CH == 2) st_stream_u32(p, __byte_perm(e[0], e[1], 0x5410));
+    else if constexpr (CH == 4) st_stream_v2(p, __byte_perm(e[0], e[1], 0x5410), __byte_perm(e[2], e[3], 0x5410));
+    else st_stream_v4(p, __byte_perm(e[0], e[1], 0x5410), __byte_perm(e[2], e[3], 0x5410),
+                      __byte_perm(e[4], e[5], 0x5410), __byte_perm(e[6], e[7], 0x5410));
+}
+
+// One symbol of one sub-stream.  Returns the table entry with the symbol in its low 16 bits.
+template <int L, bool ESC>
+__device__ __forceinline__ uint32_t decode_one(BitWin& w, const uint32_t* __restrict__ tbl, uint32_t ctx_base) {
+    const uint32_t e = tbl[ctx_base + (w.hi >> (32 - L))];
+    if constexpr (!ESC) {
+        win_consume(w, e >> 16);
+        return e;
+    } else {
+        win_consume(w, (e >> 16) & 0xFu);
+        if ((int32_t)e < 0) {  // raw 16-bit symbol follows the ESC code
+            const uint32_t raw = w.hi >> 16;
+            win_consume(w, 16);
+            return raw;
+        }
+        return e;
+    }
+}
+
+template <int L>
+__device__ __forceinline__ uint32_t ctx_base_of(uint32_t byte) {
+    if constexpr (L == 7) return byte << 7;
+    else return (byte & 0xFu) << 11;
+}
+
+// Vector path: CH adjacent sub-streams per thread, all CH elements of a step contiguous in memory.
+template <int L, int CH, bool ESC>
+__device__ __forceinline__ void decode_vec(const Smem& sm, const uint8_t* __restrict__ ctx_bytes,
+                                           uint16_t* __restrict__ out, const uint32_t* __restrict__ bs32, uint32_t lim,
+                                           const uint32_t* __restrict__ startbit, uint32_t t0, uint32_t k_eff,
+                                           uint32_t col_len, uint32_t nrows, uint32_t total) {
+    constexpr int RP = ESC ? 1 : (32 / L);  // symbols between refill checks
+    using CT = typename Ctx<CH>::T;
+    BitWin w[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) win_init(w[c], bs32, lim, startbit[t0 + c]);
+
+    const uint32_t nsteps = (total - t0 - 1) / k_eff + 1;  // t0 < k_eff <= total
+    // (row, col) walk of the prefetcher; division only here, then incremental
+    uint32_t p_rr = t0 / col_len;
+    uint32_t p_cc = t0 - p_rr * col_len;
+    uint32_t p_base = (uint32_t)sm.rowbase[p_rr];
+
+    uint32_t off[kSteps], noff[kSteps];
+    CT val[kSteps], nval[kSteps];
+    auto fetch = [&](uint32_t s, uint32_t& o, CT& v) {
+        if (s < nsteps) {
+            o = p_base + p_cc;
+            v = Ctx<CH>::ld(ctx_bytes + o);
+            p_cc += k_eff;
+            if (p_cc >= col_len) {
+                do { p_cc -= col_len; ++p_rr; } while (p_cc >= col_len);
+                p_base = (p_rr < nrows) ? (uint32_t)sm.rowbase[p_rr] : 0u;
+            }
+        }
+    };
+#pragma unroll
+    for (int u = 0; u < kSteps; ++u) fetch((uint32_t)u, off[u], val[u]);
+
+    auto step = [&](int u, bool check_refill) {
+        uint32_t e[CH];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) e[c] = decode_one<L, ESC>(w[c], sm.tbl, ctx_base_of<L>(Ctx<CH>::byte(val[u], c)));
+        store_syms<CH>(out + off[u], e);
+        if (check_refill) {
+#pragma unroll
+            for (int c = 0; c < CH; ++c)
+                if (w[c].avail <= 32) win_refill(w[c], bs32, lim);
+        }
+    };
+
+    uint32_t s0 = 0;
+    for (; s0 + kSteps <= nsteps; s0 += kSteps) {
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) fetch(s0 + kSteps + u, noff[u], nval[u]);
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) step(u, (u % RP) == RP - 1);
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) { off[u] = noff[u]; val[u] = nval[u]; }
+    }
+    // tail (< kSteps steps): the block's context bytes are already in off/val
+#pragma unroll
+    for (int u = 0; u < kSteps; ++u)
+        if (s0 + u < nsteps) step(u, (u % RP) == RP - 1);
+}
+
+// Generic path: any shape and alignment, one element at a time, 64-bit indices, per-element checks.
+template <int L>
+__device__ void decode_generic(const Smem& sm, const mps_bucket_tensor& T, int mode, const uint32_t* __restrict__ bs32,
+                               uint32_t lim, const uint32_t* __restrict__ startbit, uint32_t t_begin, uint32_t t_end,
+                               uint32_t k_eff, long long col_len, long long col_start, long long row_a,
+                               long long nrows, long long total) {
+    for (uint32_t t = t_begin; t < t_end; ++t) {
+        BitWin w;
+        win_init(w, bs32, lim, startbit[t]);
+        for (long long e = t; e < total; e += k_eff) {
+            const long long rr = e / col_len, cc = e - rr * col_len;
+            long long base;
+            if (rr < kRowCap) base = sm.rowbase[rr];
+            else {
+                const long long row = T.row_indices[row_a + rr];
+                const long long c0 = (mode == 2) ? (long long)T.group_col_start[row_a + rr] : col_start;
+                const bool ok = row >= 0 && row < T.n && c0 >= 0 && c0 + col_len <= T.m;
+                base = ok ? row * T.m + c0 : -1;
+            }
+            (void)nrows;
+            uint32_t ctx = 0;
+            if (base >= 0) ctx = T.ctx_bytes[base + cc];
+            const uint32_t sym = decode_one<L, true>(w, sm.tbl, ctx_base_of<L>(ctx)) & 0xFFFFu;
+            if (base >= 0) T.out[base + cc] = (uint16_t)sym;
+            if (w.avail <= 32) win_refill(w, bs32, lim);
+        }
+    }
+}
+
+// Fuse the bucket's tables into shared memory; returns whether any entry is an ESC.
+template <int L, int THREADS>
+__device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& T, int tid) {
+    constexpr int TS = 1 << L;                 // entries per table
+    constexpr int GROUPS_PER_CTX = TS / 8;     // 8 entries per thread-iteration
+    constexpr int NGROUPS = kTableEntries / 8;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(T.decode_syms) & 15u) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(T.decode_lens) & 3u) == 0);
+    bool esc = false;
+    for (int g = tid; g < NGROUPS; g += THREADS) {
+        const int ctx = g / GROUPS_PER_CTX;
+        const int j0 = (g - ctx * GROUPS_PER_CTX) * 8;
+        const int32_t gid = sm.gid[ctx];
+        uint32_t ent[8];
+        if (gid >= 0) {
+            uint32_t s[4], ln;
+            const uint16_t* sp = T.decode_syms + (long long)gid * TS + j0;
+            const uint8_t* lp = T.decode_lens + (long long)gid * (TS / 2) + (j0 >> 1);
+            if (aligned) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(sp));
+                s[0] = v.x; s[1] = v.y; s[2] = v.z; s[3] = v.w;
+                ln = __ldg(reinterpret_cast<const uint32_t*>(lp));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s[i] = (uint32_t)sp[2 * i] | ((uint32_t)sp[2 * i + 1] << 16);
+                ln = (uint32_t)lp[0] | ((uint32_t)lp[1] << 8) | ((uint32_t)lp[2] << 16) | ((uint32_t)lp[3] << 24);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t sym = (s[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+                const uint32_t nib = (ln >> (4 * i)) & 0xFu;
+                uint32_t len, e;
+                if constexpr (L == 7) { len = nib & 7u; e = nib >> 3; }   // bit 3 = ESC, low 3 bits = code length
+                else { e = (nib == 15u); len = e ? (uint32_t)L : nib; }    // nibble 15 = ESC with an L-bit code
+                esc |= (e != 0);
+                ent[i] = sym | (len << 16) | (e << 31);
+            }
+        } else {
+            // no table for this context: the FP8 decoder emits zeros and consumes nothing
+            // (decode_huffman.cu:252-264); the AWQ decoders treat it as an ESC (:476-485).
+            const uint32_t fill = (L == 7) ? 0u : (((uint32_t)L << 16) | 0x80000000u);
+            esc |= (L != 7);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ent[i] = fill;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(&sm.tbl[ctx * TS + j0]);
+        dst[0] = make_uint4(ent[0], ent[1], ent[2], ent[3]);
+        dst[1] = make_uint4(ent[4], ent[5], ent[6], ent[7]);
+    }
+    return __syncthreads_or(esc ? 1 : 0) != 0;
+}
+
+template <int L, int THREADS, int CH>
+__global__ void __launch_bounds__(THREADS, 1)
+bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __restrict__ ws) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+    constexpr int NCTX = (L == 7) ? 256 : 16;
+    constexpr uint32_t SPAN = THREADS * CH;  // sub-streams per work item
+    const int tid = threadIdx.x;
+
+    const bool prefix_cached = args.tensors != nullptr && args.count <= kPrefixCap;
+    if (prefix_cached)
+        for (int i = tid; i <= args.count; i += THREADS) sm.prefix[i] = args.item_prefix[i];
+    if (tid == 0) sm.staged_tensor = -1;
+    __syncthreads();
+
+    bool staged_esc = false;
+    for (;;) {
+        if (tid == 0) sm.item = (int)atomicAdd(&ws[0], 1u);
+        __syncthreads();
+        const int item = sm.item;
+        if (item >= args.total_items) break;
+
+        // ---- item -> (tensor, bucket, chunk) --------------------------------------------------
+        int ti = 0;
+        long long local = item;
+        if (args.tensors != nullptr) {
+            int lo = 0, hi = args.count;  // largest ti with prefix[ti] <= item
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                const long long p = prefix_cached ? sm.prefix[mid] : args.item_prefix[mid];
+                if (p <= item) lo = mid; else hi = mid;
+            }
+            ti = lo;
+            local = item - (prefix_cached ? sm.prefix[ti] : args.item_prefix[ti]);
+        }
+        const mps_bucket_tensor& T = (args.tensors != nullptr) ? args.tensors[ti] : args.single;
+        const int mode = T.mode;
+        const uint32_t k = (uint32_t)T.k;
+        const uint32_t chunks = (k + SPAN - 1) / SPAN;
+        const long long b = local / chunks;
+        const uint32_t chunk = (uint32_t)(local - b * chunks);
+
+        // ---- bucket geometry ------------------------------------------------------------------
+        const long long row_a = T.bucket_row_offsets[b];
+        const long long nrows = (long long)T.bucket_row_offsets[b + 1] - row_a;
+        long long col_start = 0, col_len = T.group_size;
+        if (mode != 2) { col_start = T.bucket_col_start[b]; col_len = T.bucket_col_len[b]; }
+        const long long total = nrows * col_len;
+        bool ok = nrows > 0 && col_len > 0 && row_a >= 0 && row_a + nrows <= T.num_rows &&
+                  (mode == 2 || (col_start >= 0 && col_start + col_len <= T.m));
+        const long long bit_base = T.bucket_bit_base[b];
+        const long long wb = bit_base >> 6;
+        ok = ok && bit_base >= 0 && wb < T.bitstream_words;
+        uint32_t k_eff = k;
+        if (total < (long long)k_eff) k_eff = (uint32_t)(total > 0 ? total : 1);
+        const uint32_t t_begin = chunk * SPAN;
+        if (!ok || t_begin >= k_eff) { __syncthreads(); continue; }  // uniform across the CTA
+
+        // ---- tables: restage only when the context->table map changed ----------------------------
+        constexpr int CPT = (NCTX + THREADS - 1) / THREADS;  // contexts per thread
+        int differs = (sm.staged_tensor != ti);
+        int32_t my_gid[CPT];
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            const int c = tid + i * THREADS;
+            my_gid[i] = -1;
+            if (c < NCTX) {
+                my_gid[i] = T.bucket_table[b * NCTX + c];
+                if (my_gid[i] >= T.num_tables) my_gid[i] = -1;
+                differs |= (my_gid[i] != sm.gid[c]);
+            }
+        }
+        differs = __syncthreads_or(differs);
+        if (differs) {
+#pragma unroll
+            for (int i = 0; i < CPT; ++i) {
+                const int c = tid + i * THREADS;
+                if (c < NCTX) sm.gid[c] = my_gid[i];
+            }
+            if (tid == 0) sm.staged_tensor = ti;
+            __syncthreads();
+            staged_esc = stage_tables<L, THREADS>(sm, T, tid);
+        }
+
+        // ---- row bases (element offset of each row / group start) ----------------------------------
+        int rows_ok = 1, rows_vec = 1;
+        const long long ncache = nrows < kRowCap ? nrows : kRowCap;
+        for (long long i = tid; i < ncache; i += THREADS) {
+            const long long row = T.row_indices[row_a + i];
+            const long long c0 = (mode == 2) ? (long long)T.group_col_start[row_a + i] : col_start;
+            const bool good = row >= 0 && row < T.n && c0 >= 0 && c0 + col_len <= T.m;
+            const long long base = row * T.m + c0;
+            sm.rowbase[i] = good ? base : -1;
+            rows_ok &= good;
+            rows_vec &= ((base & (CH - 1)) == 0);
+        }
+        rows_ok = __syncthreads_and(rows_ok);
+        rows_vec = __syncthreads_and(rows_vec);
+
+        const uint32_t* bs32 = reinterpret_cast<const uint32_t*>(T.bitstream) + 2 * wb;
+        const long long units = 2 * (T.bitstream_words - wb);
+        const uint32_t lim = (uint32_t)((units > 0x7FFFFFFELL ? 0x7FFFFFFELL : units) - 1);  // odd: r <= lim <=> r^1 <= lim
+        const uint32_t* startbit = T.thread_startbit + b * ((long long)k + 1);
+
+        const bool vec = rows_ok && rows_vec && nrows <= kRowCap && (k_eff % CH) == 0 && (col_len % CH) == 0 &&
+                         T.n * T.m <= 0xFFFFFFFFLL && ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & (CH - 1)) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(T.out) & (2 * CH - 1)) == 0);
+        const uint32_t t0 = t_begin + (uint32_t)tid * CH;
+        if (vec) {
+            if (t0 < k_eff) {
+                if (staged_esc)
+                    decode_vec<L, CH, true>(sm, T.ctx_bytes, T.out, bs32, lim, startbit, t0, k_eff, (uint32_t)col_len,
+                                            (uint32_t)nrows, (uint32_t)total);
+                else
+                    decode_vec<L, CH, false>(sm, T.ctx_bytes, T.out, bs32, lim, startbit, t0, k_eff, (uint32_t)col_len,
+                                             (uint32_t)nrows, (uint32_t)total);
+            }
+        } else if (t0 < k_eff) {
+            const uint32_t t1 = (t0 + CH < k_eff) ? t0 + CH : k_eff;
+            decode_generic<L>(sm, T, mode, bs32, lim, startbit, t0, t1, k_eff, col_len, col_start, row_a, nrows, total);
+        }
+        __syncthreads();  // everyone is done with tbl / rowbase / item before they are overwritten
+    }
+
+    // last CTA out re-zeroes the queue so the next launch on this stream can reuse the workspace
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned int done = atomicAdd(&ws[1], 1u);
+        if (done == gridDim.x - 1) {
+            ws[0] = 0u;
+            ws[1] = 0u;
+            __threadfence();
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+static int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+template <int L, int THREADS, int CH>
+static int launch_cfg(const BatchArgs& a, unsigned int* ws, cudaStream_t st) {
+    static bool attr_set[64] = {false};  // per instantiation and device
+    const size_t smem = sizeof(Smem);
+    int dev = 0;
+    MPS_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        MPS_CUDA_TRY(cudaFuncSetAttribute(bucket_decode_kernel<L, THREADS, CH>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    int grid = sm_count();
+    if (a.total_items < grid) grid = a.total_items;
+    if (grid <= 0) return MPS_OK;
+    bucket_decode_kernel<L, THREADS, CH><<<grid, THREADS, smem, st>>>(a, ws);
+    MPS_CUDA_TRY(cudaGetLastError());
+    return MPS_OK;
+}
+
+template <int L>
+static int launch_L(const BatchArgs& a, int threads, int chains, unsigned int* ws, cudaStream_t st) {
+#define MPS_CASE(T_, C_) if (threads == T_ && chains == C_) return launch_cfg<L, T_, C_>(a, ws, st)
+    MPS_CASE(1024, 1);
+    MPS_CASE(512, 2);
+    MPS_CASE(512, 1);
+    MPS_CASE(256, 4);
+    MPS_CASE(256, 2);
+    MPS_CASE(256, 1);
+    MPS_CASE(128, 8);
+    MPS_CASE(128, 4);
+#undef MPS_CASE
+    set_error("unsupported decode configuration threads=%d chains=%d", threads, chains);
+    return MPS_ERR_UNSUPPORTED;
+}
+
+static int env_int(const char* name, int dflt) {
+    const char* s = getenv(name);
+    return (s && *s) ? atoi(s) : dflt;
+}
+
+// threads x chains = sub-streams per work item.  Wide items (more chains per thread) cost fewer
+// instructions per symbol; narrow items give more CTAs something to do when a launch has few
+// sub-streams in total.
+static void pick_config(long long total_substreams, int k_min, int* threads, int* chains) {
+    const int sms = sm_count();
+    int t = 256, c = 4;
+    while (c > 1 && (t * c > k_min || total_substreams / ((long long)t * c) < 2LL * sms)) c >>= 1;
+    while (t > 256 && t * c > k_min) t >>= 1;
+    const int et = env_int("MPS_DECODE_THREADS", 0), ec = env_int("MPS_DECODE_CHAINS", 0);
+    if (et > 0) t = et;
+    if (ec > 0) c = ec;
+    *threads = t;
+    *chains = c;
+}
+
+static int validate_tensor(const mps_bucket_tensor& T, int L) {
+    if (!T.ctx_bytes || !T.bitstream || !T.decode_syms || !T.decode_lens || !T.bucket_table || !T.bucket_row_offsets ||
+        !T.row_indices || !T.thread_startbit || !T.bucket_bit_base || !T.out) {
+        set_error("null device pointer in tensor descriptor");
+        return MPS_ERR_INVALID;
+    }
+    if (T.mode != 2 && (!T.bucket_col_start || !T.bucket_col_len)) { set_error("bucket_col_start/len missing"); return MPS_ERR_INVALID; }
+    if (T.mode == 2 && (!T.group_col_start || T.group_size <= 0 || T.group_size > T.m)) {
+        set_error("group_size must be in (0,m]");
+        return MPS_ERR_INVALID;
+    }
+    if (T.n <= 0 || T.m <= 0) { set_error("n,m must be > 0"); return MPS_ERR_INVALID; }
+    if (T.k <= 0 || T.k > 1024) { set_error("bucket_thread_startbit_u32 has invalid k (must be 1..1024)"); return MPS_ERR_INVALID; }
+    if (T.num_buckets < 0 || T.num_tables < 0 || T.bitstream_words < 0 || T.num_rows < 0) { set_error("negative size"); return MPS_ERR_INVALID; }
+    if ((L == 7) != (T.mode == 0)) { set_error("tensor mode does not match the table width"); return MPS_ERR_INVALID; }
+    if ((reinterpret_cast<uintptr_t>(T.bitstream) & 7u) != 0) { set_error("bitstream must be 8-byte aligned"); return MPS_ERR_INVALID; }
+    return MPS_OK;
+}
+
+static int decode_single(const mps_bucket_tensor& T, int L, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = validate_tensor(T, L);
+    if (rc) return rc;
+    if (!workspace || workspace_bytes < mps_workspace_bytes()) { set_error("workspace missing or too small"); return MPS_ERR_WORKSPACE; }
+    if (T.num_buckets == 0) return MPS_OK;
+    int threads, chains;
+    pick_config(T.num_buckets * (long long)T.k, T.k, &threads, &chains);
+    const long long chunks = ((long long)T.k + (long long)threads * chains - 1) / ((long long)threads * chains);
+    const long long items = T.num_buckets * chunks;
+    if (items > 0x7FFFFFF0LL) { set_error("too many work items"); return MPS_ERR_INVALID; }
+    BatchArgs a;
+    memset(&a, 0, sizeof(a));
+    a.single = T;
+    a.tensors = nullptr;
+    a.item_prefix = nullptr;
+    a.count = 1;
+    a.total_items = (int)items;
+    unsigned int* ws = static_cast<unsigned int*>(workspace);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return (L == 7) ? launch_L<7>(a, threads, chains, ws, st) : launch_L<11>(a, threads, chains, ws, st);
+}
+
+// ------------------------------------------------------------------------------------------------
+// checksum
+// ------------------------------------------------------------------------------------------------
+__global__ void checksum_u16_kernel(const uint16_t* __restrict__ d, long long count, unsigned long long* __restrict__ res) {
+    unsigned long long sum = 0, x = 0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        const unsigned long long v = d[i];
+        sum += v;
+        x ^= v * (unsigned long long)(i + 1);
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+        x ^= __shfl_xor_sync(0xFFFFFFFFu, x, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd(&res[0], sum);
+        atomicXor(&res[1], x);
+    }
+}
+
+}  // namespace mps
+
+// ------------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------------
+using namespace mps;
+
+extern "C" {
+
+int mps_abi_version(void) { return 1; }
+
+const char* mps_last_error(void) { return g_err; }
+
+int64_t mps_cuda_clock_rate_khz(void) {
+    int dev = 0, khz = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    e = cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(clockRate)");
+    return khz;
+}
+
+size_t mps_workspace_bytes(void) { return 256; }
+
+int mps_decode_fp8(const uint8_t* fp8_u8, const uint64_t* bitstream_u64, int64_t bitstream_words,
+                   const uint16_t* decode_syms_u16, const uint8_t* decode_lens_u8, int64_t num_tables,
+                   const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                   const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                   const int32_t* row_indices_i32, int64_t num_row_indices,
+                   const uint32_t* bucket_thread_startbit_u32, const int64_t* bucket_bit_base_i64,
+                   int64_t num_buckets, int32_t k, int64_t n, int64_t m, int64_t max_len,
+                   uint16_t* out_bf16, void* workspace, size_t workspace_bytes, void* stream) {
+    if (max_len <= 0 || max_len > 15) { set_error("max_len must be in [1,15]"); return MPS_ERR_INVALID; }
+    if (max_len != 7) { set_error("decode kernel is specialized: max_len must be 7"); return MPS_ERR_INVALID; }
+    mps_bucket_tensor T;
+    memset(&T, 0, sizeof(T));
+    T.ctx_bytes = fp8_u8; T.bitstream = bitstream_u64; T.bitstream_words = bitstream_words;
+    T.decode_syms = decode_syms_u16; T.decode_lens = decode_lens_u8; T.num_tables = num_tables;
+    T.bucket_table = bucket_table_i32; T.bucket_col_start = bucket_col_start_i32; T.bucket_col_len = bucket_col_len_i32;
+    T.bucket_row_offsets = bucket_row_offsets_i32; T.row_indices = row_indices_i32; T.num_rows = num_row_indices;
+    T.thread_startbit = bucket_thread_startbit_u32; T.bucket_bit_base = bucket_bit_base_i64;
+    T.num_buckets = num_buckets; T.k = k; T.mode = 0; T.n = n; T.m = m; T.out = out_bf16;
+    return decode_single(T, 7, workspace, workspace_bytes, stream);
+}
+
+int mps_decode_awq_int4_bucket(const uint8_t* int4_values_u8, const uint64_t* bitstream_u64, int64_t bitstream_words,
+                               const uint16_t* decode_syms_u16, const uint8_t* decode_lens_u8, int64_t num_tables,
+                               const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                               const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                               const int32_t* row_indices_i32, int64_t num_row_indices,
+                               const uint32_t* bucket_thread_startbit_u32, const int64_t* bucket_bit_base_i64,
+                               int64_t num_buckets, int32_t k, int64_t n, int64_t m, int64_t max_len,
+                               uint16_t* out_bf16, void* workspace, size_t workspace_bytes, void* stream) {
+    if (max_len <= 0 || max_len > 15) { set_error("max_len must be in [1,15]"); return MPS_ERR_INVALID; }
+    if (max_len != 11) { set_error("AWQ bucket decode kernel is specialized: max_len must be 11"); return MPS_ERR_INVALID; }
+    mps_bucket_tensor T;
+    memset(&T, 0, sizeof(T));
+    T.ctx_bytes = int4_values_u8; T.bitstream = bitstream_u64; T.bitstream_words = bitstream_words;
+    T.decode_syms = decode_syms_u16; T.decode_lens = decode_lens_u8; T.num_tables = num_tables;
+    T.bucket_table = bucket_table_i32; T.bucket_col_start = bucket_col_start_i32; T.bucket_col_len = bucket_col_len_i32;
+    T.bucket_row_offsets = bucket_row_offsets_i32; T.row_indices = row_indices_i32; T.num_rows = num_row_indices;
+    T.thread_startbit = bucket_thread_startbit_u32; T.bucket_bit_base = bucket_bit_base_i64;
+    T.num_buckets = num_buckets; T.k = k; T.mode = 1; T.n = n; T.m = m; T.out = out_bf16;
+    return decode_single(T, 11, workspace, workspace_bytes, stream);
+}
+
+int mps_decode_awq_int4_bucket_by_scale(const uint8_t* int4_values_u8, const uint64_t* bitstream_u64,
+                                        int64_t bitstream_words, const uint16_t* decode_syms_u16,
+                                        const uint8_t* decode_lens_u8, int64_t num_tables,
+                                        const int32_t* bucket_table_i32, const int32_t* bucket_group_offsets_i32,
+                                        const int32_t* group_rows_i32, const int32_t* group_col_start_i32,
+                                        int64_t num_groups, const uint32_t* bucket_thread_startbit_u32,
+                                        const int64_t* bucket_bit_base_i64, int64_t num_buckets, int32_t k,
+                                        int64_t n, int64_t m, int64_t max_len, int64_t group_size,
+                                        uint16_t* out_bf16, void* workspace, size_t workspace_bytes, void* stream) {
+    if (max_len <= 0 || max_len > 15) { set_error("max_len must be in [1,15]"); return MPS_ERR_INVALID; }
+    if (max_len != 11) { set_error("AWQ ragged bucket decode kernel is specialized: max_len must be 11"); return MPS_ERR_INVALID; }
+    if (group_size <= 0 || group_size > m) { set_error("group_size must be in (0,m]"); return MPS_ERR_INVALID; }
+    mps_bucket_tensor T;
+    memset(&T, 0, sizeof(T));
+    T.ctx_bytes = int4_values_u8; T.bitstream = bitstream_u64; T.bitstream_words = bitstream_words;
+    T.decode_syms = decode_syms_u16; T.decode_lens = decode_lens_u8; T.num_tables = num_tables;
+    T.bucket_table = bucket_table_i32; T.bucket_row_offsets = bucket_group_offsets_i32;
+    T.row_indices = group_rows_i32; T.group_col_start = group_col_start_i32; T.num_rows = num_groups;
+    T.thread_startbit = bucket_thread_startbit_u32; T.bucket_bit_base = bucket_bit_base_i64;
+    T.num_buckets = num_buckets; T.k = k; T.group_size = (int32_t)group_size; T.mode = 2; T.n = n; T.m = m;
+    T.out = out_bf16;
+    return decode_single(T, 11, workspace, workspace_bytes, stream);
+}
+
+int mps_bucket_batch_plan(const mps_bucket_tensor* tensors_host, int count, int64_t* item_prefix_host,
+                          int32_t* threads_out, int32_t* chains_out) {
+    if (!tensors_host || count <= 0 || !item_prefix_host || !threads_out || !chains_out) {
+        set_error("mps_bucket_batch_plan: bad arguments");
+        return MPS_ERR_INVALID;
+    }
+    const int L = (tensors_host[0].mode == 0) ? 7 : 11;
+    long long subs = 0;
+    int k_min = 1024;
+    for (int i = 0; i < count; ++i) {
+        int rc = validate_tensor(tensors_host[i], L);
+        if (rc) return rc;
+        subs += tensors_host[i].num_buckets * (long long)tensors_host[i].k;
+        if (tensors_host[i].k < k_min) k_min = tensors_host[i].k;
+    }
+    int threads, chains;
+    pick_config(subs, k_min, &threads, &chains);
+    long long acc = 0;
+    for (int i = 0; i < count; ++i) {
+        item_prefix_host[i] = acc;
+        const long long span = (long long)threads * chains;
+        acc += tensors_host[i].num_buckets * ((tensors_host[i].k + span - 1) / span);
+    }
+    item_prefix_host[count] = acc;
+    if (acc > 0x7FFFFFF0LL) { set_error("too many work items"); return MPS_ERR_INVALID; }
+    *threads_out = threads;
+    *chains_out = chains;
+    return MPS_OK;
+}
+
+int mps_decode_bucket_batch(const mps_bucket_tensor* tensors_dev, const int64_t* item_prefix_dev, int count,
+                            int64_t total_items, int32_t threads, int32_t chains, int32_t mode,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+    if (!tensors_dev || !item_prefix_dev || count <= 0 || total_items < 0 || total_items > 0x7FFFFFF0LL) {
+        set_error("mps_decode_bucket_batch: bad arguments");
+        return MPS_ERR_INVALID;
+    }
+    if (!workspace || workspace_bytes < mps_workspace_bytes()) { set_error("workspace missing or too small"); return MPS_ERR_WORKSPACE; }
+    if (total_items == 0) return MPS_OK;
+    BatchArgs a;
+    memset(&a, 0, sizeof(a));
+    a.tensors = tensors_dev;
+    a.item_prefix = item_prefix_dev;
+    a.count = count;
+    a.total_items = (int)total_items;
+    unsigned int* ws = static_cast<unsigned int*>(workspace);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return (mode == 0) ? launch_L<7>(a, threads, chains, ws, st) : launch_L<11>(a, threads, chains, ws, st);
+}
+
+int mps_checksum_u16(const uint16_t* data_dev, int64_t count, uint64_t* result_dev, void* stream) {
+    if (!data_dev || !result_dev || count < 0) { set_error("mps_checksum_u16: bad arguments"); return MPS_ERR_INVALID; }
+    if (count == 0) return MPS_OK;
+    const int threads = 256;
+    long long blocks = (count + threads * 8 - 1) / (threads * 8);
+    const long long cap = (long long)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    checksum_u16_kernel<<<(int)blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        data_dev, count, reinterpret_cast<unsigned long long*>(result_dev));
+    MPS_CUDA_TRY(cudaGetLastError());
+    return MPS_OK;
+}
+
+}  // extern "C"

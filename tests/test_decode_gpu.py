@@ -1,0 +1,288 @@
+"""Parity of the CUDA decoders (called through the MPServe_cuda surface -> C ABI) with the CPU
+oracle, the golden fixtures of the reference encoder, and the original BF16 tensors.  Bit-exact."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from mpserve_b200 import api, util
+from mpserve_b200 import workloads as wl
+from oracle import oracle as orc
+from tests._util import golden_names
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = [(256, 4), (512, 2), (1024, 1), (256, 1), (256, 2), (128, 8), (128, 4), (512, 1)]
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from mpserve_b200 import _lib
+
+    _lib.load()  # fail loudly when the extension is missing
+    return torch.device("cuda:0")
+
+
+@pytest.fixture
+def force_config():
+    def _set(threads=None, chains=None):
+        for k, v in (("MPS_DECODE_THREADS", threads), ("MPS_DECODE_CHAINS", chains)):
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = str(v)
+
+    yield _set
+    _set(None, None)
+
+
+def _u16(t):
+    return t.view(torch.uint16).numpy()
+
+
+def _fp8_decode(ctx_np, art, n, m, dev):
+    import MPServe_cuda
+
+    d = util.artifacts_to_device(art, dev)
+    ctx = torch.from_numpy(np.ascontiguousarray(ctx_np)).to(dev)
+    out = MPServe_cuda.huffman_decode_fp8(*util.decode_fp8_args(ctx, d, n, m, 7))
+    torch.cuda.synchronize()
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (n, m)
+    return util.bf16_bits(out)
+
+
+def _encode_golden(g):
+    p = g.params
+    if g.kind == "fp8":
+        return orc.build_fp8(g.bf16, g.ctx, g.scales, p["max_len"], p["threads_per_block"])
+    if g.kind == "awq_bucket":
+        return orc.build_awq_bucket(g.bf16, g.ctx, g.scales, p["max_len"], p["threads_per_block"])
+    if g.kind == "awq_by_scale":
+        return orc.build_awq_by_scale(g.bf16, g.ctx, g.scales, p["max_len"], p["threads"], p["group_cap"])
+    return orc.build_awq_shared(g.bf16, g.ctx, g.scales, p["max_len"])
+
+
+# ---------------------------------------------------------------------------------------------
+# FP8
+# ---------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name", golden_names("fp8"))
+@pytest.mark.parametrize("cfg", [None, (256, 4), (1024, 1), (128, 8)])
+def test_fp8_golden(golden_cases, dev, force_config, name, cfg):
+    g = golden_cases[name]
+    art = _encode_golden(g)
+    g.check_artifacts(art)  # the inputs of this decode ARE the reference encoder's bytes
+    if cfg:
+        force_config(*cfg)
+    n, m = g.bf16.shape
+    got = _fp8_decode(g.ctx, art, n, m, dev)
+    np.testing.assert_array_equal(got, orc.decode_fp8(g.ctx, art, n, m))
+    np.testing.assert_array_equal(got, g.bf16)
+
+
+FP8_SEEDED = [
+    # n, m, dist, scale mode, k
+    (512, 1024, "normal", "tensor", 1024),
+    (300, 4096, "normal", "channel", 1024),
+    (256, 2048, "student_t", "channel", 1024),
+    (256, 512, "student_t", "block", 256),      # 128x128 blocks: col_len < k_eff multiples
+    (129, 1000, "normal", "channel", 1024),     # m % 8 != 0 for some paths, odd row count
+    (64, 250, "normal", "tensor", 1024),        # m % 4 != 0 -> generic path
+    (200, 3, "normal", "tensor", 256),          # m < 4
+    (1, 4096, "normal", "tensor", 1024),
+    (2048, 256, "normal", "tensor", 64),        # small k
+    (1024, 1024, "normal", "tensor", 1),        # k = 1
+    (512, 768, "normal", "channel", 32),
+]
+
+
+@pytest.mark.parametrize("case", FP8_SEEDED, ids=lambda c: "x".join(map(str, c)))
+def test_fp8_seeded_all_configs(dev, force_config, case):
+    n, m, dist, mode, k = case
+    c = wl.quantize_fp8(wl.random_weight(n, m, 100 + n + m, dist), mode)
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, k)
+    want = orc.decode_fp8(c.fp8_u8.numpy(), art, n, m)
+    np.testing.assert_array_equal(want, _u16(c.bf16))
+    for cfg in [None] + CONFIGS:
+        force_config(*(cfg or (None, None)))
+        got = _fp8_decode(c.fp8_u8.numpy(), art, n, m, dev)
+        np.testing.assert_array_equal(got, want, err_msg=f"config {cfg}")
+
+
+def test_fp8_esc_large(dev, force_config):
+    """Heavy-tailed per-tensor case: contexts of fp8 codes around zero hold > 128 distinct values."""
+    n, m = 2048, 2048
+    c = wl.quantize_fp8(wl.random_weight(n, m, 7, "student_t"), "tensor")
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
+    assert ((art["decode_lens_u8"] & 0x88) != 0).any(), "case was meant to contain ESC tables"
+    for cfg in (None, (256, 4), (512, 2), (256, 1)):
+        force_config(*(cfg or (None, None)))
+        got = _fp8_decode(c.fp8_u8.numpy(), art, n, m, dev)
+        np.testing.assert_array_equal(got, _u16(c.bf16), err_msg=f"config {cfg}")
+
+
+def test_fp8_config1_full_size_roundtrip(dev):
+    """BASELINE config 1 at full size: 4096x4096, N(0,0.02), per-tensor scale, k=1024."""
+    n = m = 4096
+    c = wl.quantize_fp8(wl.random_weight(n, m, 0, "normal"), "tensor")
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
+    got = _fp8_decode(c.fp8_u8.numpy(), art, n, m, dev)
+    np.testing.assert_array_equal(got, _u16(c.bf16))
+
+
+def test_fp8_repeated_calls_reuse_workspace(dev):
+    n, m = 256, 1024
+    c = wl.quantize_fp8(wl.random_weight(n, m, 3, "normal"), "channel")
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
+    for _ in range(5):
+        np.testing.assert_array_equal(_fp8_decode(c.fp8_u8.numpy(), art, n, m, dev), _u16(c.bf16))
+
+
+def test_fp8_missing_table_decodes_zero(dev):
+    """A context without a table (gid = -1) yields zeros and consumes nothing, as in the reference
+    kernel (decode_huffman.cu:252-264); the oracle does the same."""
+    n, m = 64, 256
+    c = wl.quantize_fp8(wl.random_weight(n, m, 5, "normal"), "tensor")
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 256)
+    art["bucket_table_i32"][:, 0x30:0x38] = -1
+    want = orc.decode_fp8(c.fp8_u8.numpy(), art, n, m)
+    got = _fp8_decode(c.fp8_u8.numpy(), art, n, m, dev)
+    np.testing.assert_array_equal(got, want)
+
+
+def test_fp8_corrupt_metadata_is_contained(dev):
+    """Out-of-range rows / windows / offsets must not fault: such buckets are skipped or clamped."""
+    n, m = 64, 256
+    c = wl.quantize_fp8(wl.random_weight(n, m, 6, "normal"), "channel")
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 256)
+    bad = dict(art)
+    bad["row_indices_i32"] = art["row_indices_i32"].copy()
+    bad["row_indices_i32"][0] = n + 1000
+    bad["bucket_col_len_i32"] = art["bucket_col_len_i32"].copy()
+    bad["bucket_col_len_i32"][-1] = m + 7
+    bad["bucket_thread_startbit_u32"] = art["bucket_thread_startbit_u32"].copy()
+    bad["bucket_thread_startbit_u32"][1, :] = 0xFFFFFF00
+    _fp8_decode(c.fp8_u8.numpy(), bad, n, m, dev)  # completes; content of the bad buckets is unspecified
+    # the context is still healthy afterwards
+    np.testing.assert_array_equal(_fp8_decode(c.fp8_u8.numpy(), art, n, m, dev), _u16(c.bf16))
+
+
+def test_fp8_argument_validation(dev):
+    import MPServe_cuda
+
+    n, m = 16, 64
+    c = wl.quantize_fp8(wl.random_weight(n, m, 1, "normal"), "tensor")
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 32)
+    d = util.artifacts_to_device(art, dev)
+    ctx = c.fp8_u8.to(dev)
+    args = list(util.decode_fp8_args(ctx, d, n, m, 7))
+    with pytest.raises(ValueError, match="max_len must be 7"):
+        MPServe_cuda.huffman_decode_fp8(*args[:-1], 12)
+    with pytest.raises(ValueError, match="numel must equal"):
+        MPServe_cuda.huffman_decode_fp8(*args[:-3], n + 1, m, 7)
+    bad = list(args)
+    bad[1] = d["bitstream_u64"].view(torch.int64)
+    with pytest.raises(ValueError, match="uint64"):
+        MPServe_cuda.huffman_decode_fp8(*bad)
+    bad = list(args)
+    bad[4] = d["bucket_table_i32"][:, :128].contiguous()
+    with pytest.raises(ValueError, match=r"\[B,256\]"):
+        MPServe_cuda.huffman_decode_fp8(*bad)
+
+
+def test_fp8_batch_plan_matches_single(dev):
+    shapes = [(256, 1024, "channel"), (64, 512, "tensor"), (1024, 256, "channel"), (8, 4096, "channel")]
+    entries, wants = [], []
+    for i, (n, m, mode) in enumerate(shapes):
+        c = wl.quantize_fp8(wl.random_weight(n, m, 40 + i, "normal"), mode)
+        art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
+        entries.append((c.fp8_u8.to(dev), util.artifacts_to_device(art, dev), None))
+        wants.append(_u16(c.bf16))
+    plan = api.BucketDecodePlan(entries, mode=0)
+    for _ in range(2):
+        outs = plan.decode()
+        torch.cuda.synchronize()
+        for o, w in zip(outs, wants):
+            np.testing.assert_array_equal(util.bf16_bits(o), w)
+        for o in outs:
+            o.zero_()
+
+
+# ---------------------------------------------------------------------------------------------
+# AWQ
+# ---------------------------------------------------------------------------------------------
+
+def _awq_decode(kind, ctx_np, art, n, m, dev, L=11):
+    import MPServe_cuda
+
+    d = util.artifacts_to_device(art, dev)
+    ctx = torch.from_numpy(np.ascontiguousarray(ctx_np)).to(dev)
+    if kind == "awq_bucket":
+        out = MPServe_cuda.huffman_decode_awq_int4_bucket(
+            ctx, d["bitstream_u64"], d["decode_syms_u16"], d["decode_lens_u8"], d["bucket_table_i32"],
+            d["bucket_col_start_i32"], d["bucket_col_len_i32"], d["bucket_row_offsets_i32"], d["row_indices_i32"],
+            d["bucket_thread_startbit_u32"], d["bucket_bit_base_i64"], n, m, L)
+    elif kind == "awq_by_scale":
+        out = MPServe_cuda.huffman_decode_awq_int4_bucket_by_scale(
+            ctx, d["bitstream_u64"], d["decode_syms_u16"], d["decode_lens_u8"], d["bucket_table_i32"],
+            d["bucket_group_offsets_i32"], d["group_rows_i32"], d["group_col_start_i32"],
+            d["bucket_thread_startbit_u32"], d["bucket_bit_base_i64"], n, m, L, int(art["shape_nmkg_i64"][3]))
+    else:
+        out = MPServe_cuda.huffman_decode_awq_shared_table(
+            d["bitstream_u64"], d["decode_syms_i16"], d["decode_nbits_u8"], d["scale_bit_base_i64"],
+            d["chunk_startbit_rel_u32"], d["chunk_out_base_u32"], d["chunk_meta_u32"], d["chunk_scale_id_i32"],
+            d["out_idx_i32"], d["stream_chunk_ofs_i64"], d["stream_chunk_ids_i32"], n * m, L)
+        torch.cuda.synchronize()
+        assert out.dtype == torch.int16
+        return out.cpu().numpy().view(np.uint16).reshape(n, m)
+    torch.cuda.synchronize()
+    return util.bf16_bits(out)
+
+
+@pytest.mark.parametrize("name", golden_names("awq"))
+def test_awq_golden(golden_cases, dev, name):
+    g = golden_cases[name]
+    art = _encode_golden(g)
+    g.check_artifacts(art)
+    n, m = g.bf16.shape
+    got = _awq_decode(g.kind, g.ctx, art, n, m, dev, g.params["max_len"])
+    np.testing.assert_array_equal(got, g.bf16)
+
+
+@pytest.mark.parametrize("scale_kind", ["group", "row", "scalar"])
+def test_awq_seeded(dev, force_config, scale_kind):
+    n, m = 256, 1024
+    c = wl.quantize_awq(wl.random_weight(n, m, 77, "normal"), 128)
+    sc = c.scales_u16.numpy()
+    if scale_kind == "row":
+        sc = np.ascontiguousarray(sc[:, 0])
+    elif scale_kind == "scalar":
+        sc = np.ascontiguousarray(sc[:1, 0])
+    q, b = c.int4_u8.numpy(), _u16(c.bf16)
+    arts = {
+        "awq_bucket": orc.build_awq_bucket(b, q, sc, 11, 256),
+        "awq_by_scale": orc.build_awq_by_scale(b, q, sc, 11, 256, 1024),
+        "awq_shared": orc.build_awq_shared(b, q, sc, 11),
+    }
+    for kind, art in arts.items():
+        for cfg in (None, (256, 1), (128, 4)):
+            force_config(*(cfg or (None, None)))
+            got = _awq_decode(kind, q, art, n, m, dev)
+            np.testing.assert_array_equal(got, b, err_msg=f"{kind} {cfg}")
+
+
+# ---------------------------------------------------------------------------------------------
+# checksum
+# ---------------------------------------------------------------------------------------------
+
+def test_checksum_matches_numpy(dev):
+    rng = np.random.default_rng(0)
+    a = rng.integers(0, 65536, size=1_000_003, dtype=np.uint16)
+    acc = api.checksum_u16(torch.from_numpy(a).to(dev).view(torch.bfloat16))
+    torch.cuda.synchronize()
+    got = acc.cpu().numpy().view(np.uint64)
+    want_sum = np.uint64(a.astype(np.uint64).sum())
+    want_xor = np.bitwise_xor.reduce(a.astype(np.uint64) * (np.arange(a.size, dtype=np.uint64) + np.uint64(1)))
+    assert got[0] == want_sum and got[1] == want_xor
