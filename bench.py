@@ -241,11 +241,21 @@ def run_ours(args, rank, world, local_rank):
     # ---- device-resident throughput ------------------------------------------------------------
     for _ in range(args.warmup):
         plan.decode()
+    # clocks are sampled from before an untimed pre-roll of the same launches (so that the sampler,
+    # whose period is ~100 ms, sees the load of the short timed region) until after a post-roll
     sampler = ClockSampler(local_rank)
     barrier()
     if rank == 0:
         sampler.start()
-        time.sleep(0.25)
+
+    def roll(seconds):
+        t_stop = time.perf_counter() + seconds
+        while time.perf_counter() < t_stop:
+            for _ in range(4):
+                plan.decode()
+            torch.cuda.synchronize()
+
+    roll(0.6)
     barrier()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     t_begin = torch.cuda.Event(enable_timing=True)
@@ -256,6 +266,8 @@ def run_ours(args, rank, world, local_rank):
         plan.decode()
         b.record()
     t_end.record()
+    torch.cuda.synchronize()
+    roll(0.3)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     total_ms = t_begin.elapsed_time(t_end)

@@ -40,6 +40,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
            "-Xcompiler", "-fvisibility=hidden", "--use_fast_math", "-o", str(LIB)]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("MPS_EXTRA_NVCC_FLAGS", "").split()  # tuning experiments, e.g. -DMPS_LOOK=2
     cmd += [str(CSRC / s) for s in SOURCES]
     env = dict(os.environ)
     env.pop("CC", None)

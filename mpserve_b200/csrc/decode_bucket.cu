@@ -54,6 +54,10 @@ constexpr int kTableEntries = 32768;  // 256 ctx x 2^7 == 16 ctx x 2^11
 constexpr int kRowCap = 2048;         // rows / groups of a bucket cached in shared memory
 constexpr int kPrefixCap = 1024;      // tensors of a batch whose item prefix is cached in shared memory
 constexpr int kSteps = 4;             // steps per software-pipeline block
+#ifndef MPS_LOOK
+#define MPS_LOOK 1
+#endif
+constexpr int kLook = MPS_LOOK;       // bitstream units requested ahead of use, per sub-stream
 
 struct BatchArgs {
     mps_bucket_tensor single;            // used when tensors == nullptr
@@ -64,13 +68,15 @@ struct BatchArgs {
 };
 
 struct Smem {
-    uint32_t tbl[kTableEntries];
+    uint32_t tbl[kTableEntries];   // fused entries: sym << 16 | esc << 15 | code length
     long long rowbase[kRowCap];
     int32_t gid[256];
     long long prefix[kPrefixCap + 1];
     int item;
     int staged_tensor;
 };
+
+constexpr uint32_t kEscBit = 0x8000u;
 
 template <int CH> struct Ctx;
 template <> struct Ctx<1> {
@@ -94,37 +100,84 @@ template <> struct Ctx<8> {
     static __device__ __forceinline__ uint32_t byte(T v, int c) { return (((c < 4) ? v.x : v.y) >> (8 * (c & 3))) & 0xFFu; }
 };
 
+// symbols sit in the HIGH half of an entry
 template <int CH>
 __device__ __forceinline__ void store_syms(uint16_t* p, const uint32_t (&e)[CH]) {
-    if constexpr (CH == 1) st_stream_u16(p, e[0]);
-    else if constexpr (CH == 2) st_stream_u32(p, __byte_perm(e[0], e[1], 0x5410));
-    else if constexpr (CH == 4) st_stream_v2(p, __byte_perm(e[0], e[1], 0x5410), __byte_perm(e[2], e[3], 0x5410));
-    else st_stream_v4(p, __byte_perm(e[0], e[1], 0x5410), __byte_perm(e[2], e[3], 0x5410),
-                      __byte_perm(e[4], e[5], 0x5410), __byte_perm(e[6], e[7], 0x5410));
-}
-
-// One symbol of one sub-stream.  Returns the table entry with the symbol in its low 16 bits.
-template <int L, bool ESC>
-__device__ __forceinline__ uint32_t decode_one(BitWin& w, const uint32_t* __restrict__ tbl, uint32_t ctx_base) {
-    const uint32_t e = tbl[ctx_base + (w.hi >> (32 - L))];
-    if constexpr (!ESC) {
-        win_consume(w, e >> 16);
-        return e;
-    } else {
-        win_consume(w, (e >> 16) & 0xFu);
-        if ((int32_t)e < 0) {  // raw 16-bit symbol follows the ESC code
-            const uint32_t raw = w.hi >> 16;
-            win_consume(w, 16);
-            return raw;
-        }
-        return e;
-    }
+    if constexpr (CH == 1) st_stream_u16(p, e[0] >> 16);
+    else if constexpr (CH == 2) st_stream_u32(p, __byte_perm(e[0], e[1], 0x7632));
+    else if constexpr (CH == 4) st_stream_v2(p, __byte_perm(e[0], e[1], 0x7632), __byte_perm(e[2], e[3], 0x7632));
+    else st_stream_v4(p, __byte_perm(e[0], e[1], 0x7632), __byte_perm(e[2], e[3], 0x7632),
+                      __byte_perm(e[4], e[5], 0x7632), __byte_perm(e[6], e[7], 0x7632));
 }
 
 template <int L>
-__device__ __forceinline__ uint32_t ctx_base_of(uint32_t byte) {
-    if constexpr (L == 7) return byte << 7;
-    else return (byte & 0xFu) << 11;
+__device__ __forceinline__ uint32_t ctx_of(uint32_t byte) {
+    if constexpr (L == 7) return byte;
+    else return byte & 0xFu;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Fast path reader.  Decoding runs in blocks of RP = (32-L)/L + 1 symbols on a 32-bit window that
+// is rebuilt at every block start from the sub-stream's bit position and two cached 32-bit units;
+// a block consumes fewer than 32 bits, so at most one new unit is needed per block, and that unit
+// was requested LOOK blocks earlier (software prefetch: the load has whole blocks of other work to
+// complete behind).  Everything is branch-free: the unit load is a predicated instruction, the
+// register rotation is selects, so the CH chains of a thread interleave freely.  Within a block a
+// symbol costs: one funnel shift that fuses context and prefix into the table index, one shift to a
+// byte address, one shared-memory load, one shift of the window by the entry's low bits, one add
+// that accumulates the code lengths in the low half of a register.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint32_t lds_table(uint32_t addr) {  // the table is constant while decoding
+    uint32_t v;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// Unit r of the stream (bit order) is bs32[r ^ 1]; clamped to the last valid unit.  On an L2 miss
+// the whole 128-byte line is brought into L2: the seven following sectors of this sub-stream
+// then hit L2 (each sub-stream walks its own line, so L1 cannot hold all of them).
+__device__ __forceinline__ uint32_t unit_addr_ofs(uint32_t r, uint32_t lim) { return min(r ^ 1u, lim); }
+
+__device__ __forceinline__ uint32_t ld_unit_l2(const uint32_t* __restrict__ bs32, uint32_t r, uint32_t lim) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L2::128B.u32 %0, [%1];" : "=r"(v) : "l"(bs32 + unit_addr_ofs(r, lim)));
+    return v;
+}
+__device__ __forceinline__ void ld_unit_l2_if(uint32_t& v, const uint32_t* __restrict__ bs32, uint32_t r, uint32_t lim,
+                                              uint32_t pred) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %2, 0;\n\t@p ld.global.nc.L2::128B.u32 %0, [%1];\n\t}"
+        : "+r"(v)
+        : "l"(bs32 + unit_addr_ofs(r, lim)), "r"(pred));
+}
+
+template <int LOOK>
+struct Chain {
+    uint32_t pos;           // bit position relative to bs32
+    uint32_t w[2 + LOOK];   // units pos>>5, +1, and LOOK prefetched ones
+};
+
+template <int LOOK>
+__device__ __forceinline__ void chain_init(Chain<LOOK>& ch, const uint32_t* __restrict__ bs32, uint32_t lim, uint32_t pos) {
+    ch.pos = pos;
+    const uint32_t u = pos >> 5;
+#pragma unroll
+    for (int i = 0; i < 2 + LOOK; ++i) ch.w[i] = ld_unit_l2(bs32, u + i, lim);
+}
+
+// Advance by `used` (< 32) bits and return the fresh 32-bit window.
+template <int LOOK>
+__device__ __forceinline__ uint32_t chain_window(Chain<LOOK>& ch, const uint32_t* __restrict__ bs32, uint32_t lim,
+                                                 uint32_t used) {
+    const uint32_t np = ch.pos + used;
+    const uint32_t cross = ((np ^ ch.pos) > 31u) ? 1u : 0u;  // moved into the next unit
+    ch.pos = np;
+#pragma unroll
+    for (int i = 0; i < 1 + LOOK; ++i) ch.w[i] = cross ? ch.w[i + 1] : ch.w[i];
+    ld_unit_l2_if(ch.w[1 + LOOK], bs32, (np >> 5) + 1 + LOOK, lim, cross);
+    return __funnelshift_l(ch.w[1], ch.w[0], np);
 }
 
 // Vector path: CH adjacent sub-streams per thread, all CH elements of a step contiguous in memory.
@@ -133,20 +186,21 @@ __device__ __forceinline__ void decode_vec(const Smem& sm, const uint8_t* __rest
                                            uint16_t* __restrict__ out, const uint32_t* __restrict__ bs32, uint32_t lim,
                                            const uint32_t* __restrict__ startbit, uint32_t t0, uint32_t k_eff,
                                            uint32_t col_len, uint32_t nrows, uint32_t total) {
-    constexpr int RP = ESC ? 1 : (32 / L);  // symbols between refill checks
+    constexpr int RP = ESC ? 1 : ((32 - L) / L + 1);  // symbols per 32-bit window
+    constexpr int LOOK = kLook;
+    static_assert(kSteps % RP == 0, "a block of steps must hold whole windows");
     using CT = typename Ctx<CH>::T;
-    BitWin w[CH];
+    const uint32_t tbl = smem_u32(sm.tbl);
+
+    Chain<LOOK> ch[CH];
 #pragma unroll
-    for (int c = 0; c < CH; ++c) win_init(w[c], bs32, lim, startbit[t0 + c]);
+    for (int c = 0; c < CH; ++c) chain_init(ch[c], bs32, lim, startbit[t0 + c]);
 
     const uint32_t nsteps = (total - t0 - 1) / k_eff + 1;  // t0 < k_eff <= total
     // (row, col) walk of the prefetcher; division only here, then incremental
     uint32_t p_rr = t0 / col_len;
     uint32_t p_cc = t0 - p_rr * col_len;
     uint32_t p_base = (uint32_t)sm.rowbase[p_rr];
-
-    uint32_t off[kSteps], noff[kSteps];
-    CT val[kSteps], nval[kSteps];
     auto fetch = [&](uint32_t s, uint32_t& o, CT& v) {
         if (s < nsteps) {
             o = p_base + p_cc;
@@ -158,34 +212,76 @@ __device__ __forceinline__ void decode_vec(const Smem& sm, const uint8_t* __rest
             }
         }
     };
+    uint32_t offA[kSteps], offB[kSteps];
+    CT valA[kSteps], valB[kSteps];
 #pragma unroll
-    for (int u = 0; u < kSteps; ++u) fetch((uint32_t)u, off[u], val[u]);
+    for (int u = 0; u < kSteps; ++u) fetch((uint32_t)u, offA[u], valA[u]);
 
-    auto step = [&](int u, bool check_refill) {
-        uint32_t e[CH];
+    uint32_t hi[CH], acc[CH];
 #pragma unroll
-        for (int c = 0; c < CH; ++c) e[c] = decode_one<L, ESC>(w[c], sm.tbl, ctx_base_of<L>(Ctx<CH>::byte(val[u], c)));
-        store_syms<CH>(out + off[u], e);
-        if (check_refill) {
+    for (int c = 0; c < CH; ++c) acc[c] = 0;
+
+    // `count` (<= kSteps) steps from one prefetched block
+    auto run = [&](const uint32_t (&off)[kSteps], const CT (&val)[kSteps], uint32_t count) {
 #pragma unroll
-            for (int c = 0; c < CH; ++c)
-                if (w[c].avail <= 32) win_refill(w[c], bs32, lim);
+        for (int u = 0; u < kSteps; ++u) {
+            if ((uint32_t)u < count) {
+                if (u % RP == 0) {
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) {
+                        hi[c] = chain_window(ch[c], bs32, lim, acc[c] & 0xFFFFu);
+                        acc[c] = 0;
+                    }
+                }
+                uint32_t e[CH];
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                    // index = ctx << L | top L bits of the window, in one funnel shift
+                    const uint32_t idx = __funnelshift_l(hi[c], ctx_of<L>(Ctx<CH>::byte(val[u], c)), L);
+                    e[c] = lds_table(tbl + (idx << 2));
+                    if constexpr (!ESC) {
+                        hi[c] = __funnelshift_l(0u, hi[c], e[c]);  // shift by the low 5 bits = code length
+                        acc[c] += e[c];                            // low half accumulates the lengths
+                    } else {
+                        uint32_t used = e[c] & 0xFu;
+                        if (e[c] & kEscBit) {                     // 16 raw bits follow the ESC code
+                            e[c] = __funnelshift_l(0u, hi[c], used) & 0xFFFF0000u;
+                            used += 16;
+                        }
+                        acc[c] = used;
+                    }
+                }
+                store_syms<CH>(out + off[u], e);
+            }
         }
     };
 
     uint32_t s0 = 0;
-    for (; s0 + kSteps <= nsteps; s0 += kSteps) {
+    for (;;) {
+        if (s0 + kSteps > nsteps) { run(offA, valA, nsteps - s0); break; }
 #pragma unroll
-        for (int u = 0; u < kSteps; ++u) fetch(s0 + kSteps + u, noff[u], nval[u]);
+        for (int u = 0; u < kSteps; ++u) fetch(s0 + kSteps + u, offB[u], valB[u]);
+        run(offA, valA, kSteps);
+        s0 += kSteps;
+        if (s0 + kSteps > nsteps) { run(offB, valB, nsteps - s0); break; }
 #pragma unroll
-        for (int u = 0; u < kSteps; ++u) step(u, (u % RP) == RP - 1);
-#pragma unroll
-        for (int u = 0; u < kSteps; ++u) { off[u] = noff[u]; val[u] = nval[u]; }
+        for (int u = 0; u < kSteps; ++u) fetch(s0 + kSteps + u, offA[u], valA[u]);
+        run(offB, valB, kSteps);
+        s0 += kSteps;
     }
-    // tail (< kSteps steps): the block's context bytes are already in off/val
-#pragma unroll
-    for (int u = 0; u < kSteps; ++u)
-        if (s0 + u < nsteps) step(u, (u % RP) == RP - 1);
+}
+
+// One symbol with the register bit window (generic path).  Returns the 16-bit symbol.
+template <int L>
+__device__ __forceinline__ uint32_t decode_one_win(BitWin& w, const uint32_t* __restrict__ tbl, uint32_t ctx) {
+    const uint32_t e = tbl[(ctx << L) + (w.hi >> (32 - L))];
+    win_consume(w, e & 0xFu);
+    if (e & kEscBit) {
+        const uint32_t raw = w.hi >> 16;
+        win_consume(w, 16);
+        return raw;
+    }
+    return e >> 16;
 }
 
 // Generic path: any shape and alignment, one element at a time, 64-bit indices, per-element checks.
@@ -193,7 +289,7 @@ template <int L>
 __device__ void decode_generic(const Smem& sm, const mps_bucket_tensor& T, int mode, const uint32_t* __restrict__ bs32,
                                uint32_t lim, const uint32_t* __restrict__ startbit, uint32_t t_begin, uint32_t t_end,
                                uint32_t k_eff, long long col_len, long long col_start, long long row_a,
-                               long long nrows, long long total) {
+                               long long total) {
     for (uint32_t t = t_begin; t < t_end; ++t) {
         BitWin w;
         win_init(w, bs32, lim, startbit[t]);
@@ -207,10 +303,9 @@ __device__ void decode_generic(const Smem& sm, const mps_bucket_tensor& T, int m
                 const bool ok = row >= 0 && row < T.n && c0 >= 0 && c0 + col_len <= T.m;
                 base = ok ? row * T.m + c0 : -1;
             }
-            (void)nrows;
             uint32_t ctx = 0;
             if (base >= 0) ctx = T.ctx_bytes[base + cc];
-            const uint32_t sym = decode_one<L, true>(w, sm.tbl, ctx_base_of<L>(ctx)) & 0xFFFFu;
+            const uint32_t sym = decode_one_win<L>(w, sm.tbl, ctx_of<L>(ctx));
             if (base >= 0) T.out[base + cc] = (uint16_t)sym;
             if (w.avail <= 32) win_refill(w, bs32, lim);
         }
@@ -252,12 +347,12 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
                 if constexpr (L == 7) { len = nib & 7u; e = nib >> 3; }   // bit 3 = ESC, low 3 bits = code length
                 else { e = (nib == 15u); len = e ? (uint32_t)L : nib; }    // nibble 15 = ESC with an L-bit code
                 esc |= (e != 0);
-                ent[i] = sym | (len << 16) | (e << 31);
+                ent[i] = (sym << 16) | (e << 15) | len;
             }
         } else {
             // no table for this context: the FP8 decoder emits zeros and consumes nothing
             // (decode_huffman.cu:252-264); the AWQ decoders treat it as an ESC (:476-485).
-            const uint32_t fill = (L == 7) ? 0u : (((uint32_t)L << 16) | 0x80000000u);
+            const uint32_t fill = (L == 7) ? 0u : ((uint32_t)L | kEscBit);
             esc |= (L != 7);
 #pragma unroll
             for (int i = 0; i < 8; ++i) ent[i] = fill;
@@ -373,8 +468,9 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         const uint32_t lim = (uint32_t)((units > 0x7FFFFFFELL ? 0x7FFFFFFELL : units) - 1);  // odd: r <= lim <=> r^1 <= lim
         const uint32_t* startbit = T.thread_startbit + b * ((long long)k + 1);
 
-        const bool vec = rows_ok && rows_vec && nrows <= kRowCap && (k_eff % CH) == 0 && (col_len % CH) == 0 &&
-                         T.n * T.m <= 0xFFFFFFFFLL && ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & (CH - 1)) == 0) &&
+        const bool vec = rows_ok && rows_vec && nrows <= kRowCap && (k_eff % CH) == 0 &&
+                         (col_len % CH) == 0 && T.n * T.m <= 0xFFFFFFFFLL &&
+                         ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & (CH - 1)) == 0) &&
                          ((reinterpret_cast<uintptr_t>(T.out) & (2 * CH - 1)) == 0);
         const uint32_t t0 = t_begin + (uint32_t)tid * CH;
         if (vec) {
@@ -388,7 +484,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             }
         } else if (t0 < k_eff) {
             const uint32_t t1 = (t0 + CH < k_eff) ? t0 + CH : k_eff;
-            decode_generic<L>(sm, T, mode, bs32, lim, startbit, t0, t1, k_eff, col_len, col_start, row_a, nrows, total);
+            decode_generic<L>(sm, T, mode, bs32, lim, startbit, t0, t1, k_eff, col_len, col_start, row_a, total);
         }
         __syncthreads();  // everyone is done with tbl / rowbase / item before they are overwritten
     }
