@@ -51,11 +51,14 @@ int cuda_fail(cudaError_t e, const char* what) {
 // kernel
 // ------------------------------------------------------------------------------------------------
 constexpr int kTableEntries = 32768;  // 256 ctx x 2^7 == 16 ctx x 2^11
-constexpr int kRowCap = 2048;         // rows / groups of a bucket cached in shared memory
-constexpr int kPrefixCap = 1024;      // tensors of a batch whose item prefix is cached in shared memory
+constexpr int kRowCap = 1024;         // rows / groups of a bucket cached in shared memory
+constexpr int kPrefixCap = 512;       // tensors of a batch whose item prefix is cached in shared memory
 constexpr int kSteps = 4;             // steps per software-pipeline block
 #ifndef MPS_LOOK
 #define MPS_LOOK 1
+#endif
+#ifndef MPS_NO_STREAM
+#define MPS_NO_STREAM 0
 #endif
 constexpr int kLook = MPS_LOOK;       // bitstream units requested ahead of use, per sub-stream
 
@@ -67,16 +70,43 @@ struct BatchArgs {
     int total_items;
 };
 
+#ifndef MPS_STAGES
+#define MPS_STAGES 8
+#endif
+constexpr int kStages = MPS_STAGES;            // context-byte ring: stages of kSteps steps each
+constexpr int kMaxSpan = 1024;        // sub-streams per work item (threads x chains), at most
+
 struct Smem {
-    uint32_t tbl[kTableEntries];   // fused entries: sym << 16 | esc << 15 | code length
+    uint32_t tbl[kTableEntries];                 // fused entries: sym << 16 | esc << 15 | code length
+    uint4 bitring[2 * kMaxSpan];                 // per sub-stream: two 16-byte halves of its bitstream
+    uint8_t ctxring[kStages * kSteps * kMaxSpan];  // context bytes of the next kStages blocks of steps
     long long rowbase[kRowCap];
-    int32_t gid[256];
     long long prefix[kPrefixCap + 1];
+    unsigned long long full_bar[kStages];        // bulk copies of a stage have landed
+    unsigned long long empty_bar[kStages];       // every warp is done reading a stage
+    int32_t gid[256];
     int item;
     int staged_tensor;
+    int abort;                                   // a bounded wait gave up
 };
 
 constexpr uint32_t kEscBit = 0x8000u;
+
+// Optional per-phase cycle counters (tuning builds only: -DMPS_PHASE_TIMERS): thread 0 of every CTA
+// adds its clock deltas to ws[8 + 2*phase] (64-bit) so a host script can print the split.
+#ifdef MPS_PHASE_TIMERS
+#define MPS_T0() long long _t_prev = clock64()
+#define MPS_TICK(phase)                                                                       \
+    do {                                                                                      \
+        const long long _t_now = clock64();                                                   \
+        if (threadIdx.x == 0)                                                                 \
+            atomicAdd(reinterpret_cast<unsigned long long*>(ws + 8) + (phase), (unsigned long long)(_t_now - _t_prev)); \
+        _t_prev = _t_now;                                                                     \
+    } while (0)
+#else
+#define MPS_T0() do {} while (0)
+#define MPS_TICK(phase) do {} while (0)
+#endif
 
 template <int CH> struct Ctx;
 template <> struct Ctx<1> {
@@ -271,6 +301,284 @@ __device__ __forceinline__ void decode_vec(const Smem& sm, const uint8_t* __rest
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Streaming fast path: everything a work item reads from HBM arrives through asynchronous copies
+// into shared memory, deep enough ahead of use to cover HBM latency at full rate (Little's law
+// wants tens of KB in flight per SM; register prefetch gave a few KB).
+//
+//  * Context bytes: one elected thread issues cp.async.bulk (the TMA bulk-copy engine, no tensor
+//    map, no multicast) of the SPAN contiguous bytes every step needs, kSteps steps per stage,
+//    kStages stages ahead; stages are handed over with full/empty mbarriers.  Consumers read their
+//    CH bytes of a step with one conflict-free shared-memory load.
+//  * Bitstream: each sub-stream owns 32 bytes of shared memory (two 16-byte halves).  When its
+//    window moves into a 16-byte chunk it starts the cp.async of the following chunk into the half
+//    it just left; groups are committed once per block by every thread and awaited with
+//    cp.async.wait_group kBitLag, i.e. a copy has kBitLag whole blocks to land.  A chunk holds at
+//    least five blocks' worth of bits (a block consumes < 32 bits), so kBitLag = 4 is always safe.
+//    The divergent access (every lane a different 128-byte line) thus happens once per 16 bytes
+//    (~32 symbols) per sub-stream instead of once per 4 bytes.
+// ------------------------------------------------------------------------------------------------
+#ifndef MPS_BITLAG
+#define MPS_BITLAG 4
+#endif
+constexpr int kBitLag = MPS_BITLAG;
+constexpr uint32_t kSpinLimit = 1u << 22;  // bounded waits: give up, flag, return
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Returns false when the barrier did not complete within the spin limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16_if(uint32_t dst, const void* src, uint32_t pred) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %2, 0;\n\t@p cp.async.cg.shared.global [%0], [%1], 16;\n\t}"
+                 ::"r"(dst), "l"(src), "r"(pred) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t lds_ordered(uint32_t addr) {  // ordered with the async copies
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void lds_ordered_if(uint32_t& v, uint32_t addr, uint32_t pred) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %2, 0;\n\t@p ld.shared.u32 %0, [%1];\n\t}"
+                 : "+r"(v) : "r"(addr), "r"(pred) : "memory");
+}
+
+struct BitOrigin {        // bitstream of the item seen from a 16-byte aligned origin
+    const uint8_t* base;  // 16-byte aligned
+    uint32_t bytes;       // valid bytes from base
+    uint32_t bit_delta;   // bits between the origin and the bucket's first bit (0 or 64)
+};
+
+// 32-bit unit x (bit order) of the stream sits at byte 4*(x^1); the ring keeps byte offsets mod 32.
+__device__ __forceinline__ uint32_t ring_unit_addr(uint32_t ring, uint32_t x) { return ring + (((x ^ 1u) & 7u) << 2); }
+
+struct SChain {
+    uint32_t pos;     // bit position relative to BitOrigin::base
+    uint32_t w0, w1;  // units pos>>5 and (pos>>5)+1
+};
+
+// Move by `used` (< 32) bits; returns the fresh 32-bit window.  When w1 becomes the first unit of
+// a 16-byte chunk, the copy of the following chunk is started (predicated, no branch).
+__device__ __forceinline__ uint32_t schain_window(SChain& ch, uint32_t ring, const BitOrigin& bo, uint32_t used) {
+    const uint32_t np = ch.pos + used;
+    const uint32_t cross = ((np ^ ch.pos) > 31u) ? 1u : 0u;
+    const uint32_t x = (np >> 5) + 1;  // unit that w1 must hold
+    ch.pos = np;
+    ch.w0 = cross ? ch.w1 : ch.w0;
+    lds_ordered_if(ch.w1, ring_unit_addr(ring, x), cross);
+    const uint32_t ofs = (x << 2) + 16u;  // byte offset of the chunk after x's, valid when x % 4 == 0
+    const uint32_t fetch = (cross && (x & 3u) == 0u && ofs + 16u <= bo.bytes) ? 1u : 0u;
+    cp_async_16_if(ring + (ofs & 16u), bo.base + ofs, fetch);
+    return __funnelshift_l(ch.w1, ch.w0, np);
+}
+
+template <int CH>
+__device__ __forceinline__ typename Ctx<CH>::T lds_ctx(uint32_t addr) {
+    if constexpr (CH == 8) {
+        uint2 v;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
+        return v;
+    } else {
+        uint32_t v;
+        if constexpr (CH == 4) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+        else if constexpr (CH == 2) asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+        else asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+        return v;
+    }
+}
+
+// Geometry of one work item on the streaming path (uniform across the CTA).
+struct StreamItem {
+    const uint8_t* ctx_bytes;
+    uint16_t* out;
+    const uint32_t* startbit;
+    BitOrigin bo;
+    uint32_t t_begin, k_eff, col_len, nsteps;
+};
+
+// Copies of block `jb` of the item (elected thread only).  Returns false if the stage never freed.
+template <int SPAN>
+__device__ __forceinline__ bool producer_issue(Smem& sm, const StreamItem& it, uint32_t g, uint32_t jb, uint32_t& p_rr,
+                                               uint32_t& p_cc) {
+    const uint32_t stage = g % kStages, round = g / kStages;
+    const uint32_t full = smem_u32(&sm.full_bar[stage]);
+    if (!mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u)) return false;
+    const uint32_t left = it.nsteps - jb * kSteps;
+    const uint32_t nst = left < (uint32_t)kSteps ? left : (uint32_t)kSteps;
+    mbar_expect_tx(full, nst * SPAN);
+    for (uint32_t u = 0; u < nst; ++u) {
+        const uint8_t* src = it.ctx_bytes + (uint32_t)sm.rowbase[p_rr] + p_cc + it.t_begin;
+        bulk_g2s(smem_u32(sm.ctxring) + (stage * kSteps + u) * SPAN, src, SPAN, full);
+        p_cc += it.k_eff;
+        if (p_cc >= it.col_len) { p_cc = 0; ++p_rr; }
+    }
+    return true;
+}
+
+template <int L, int THREADS, int CH>
+struct StreamThread {  // per-thread state that lives from stream_begin to stream_run
+    SChain ch[CH];
+};
+
+// Start everything that can overlap with table staging: first bitstream chunks of every
+// sub-stream, first kStages blocks of context bytes.
+template <int L, int THREADS, int CH>
+__device__ __forceinline__ bool stream_begin(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st,
+                                             uint32_t blk) {
+    constexpr uint32_t SPAN = THREADS * CH;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t ring0 = smem_u32(sm.bitring) + tid * 32u;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const uint32_t ring = ring0 + c * THREADS * 32;
+        const uint32_t pos = it.startbit[it.t_begin + tid * CH + c] + it.bo.bit_delta;
+        st.ch[c].pos = pos;
+        const uint32_t o0 = (pos >> 7) << 4, o1 = o0 + 16u;
+        cp_async_16_if(ring + (o0 & 16u), it.bo.base + o0, (o0 + 16u <= it.bo.bytes) ? 1u : 0u);
+        cp_async_16_if(ring + (o1 & 16u), it.bo.base + o1, (o1 + 16u <= it.bo.bytes) ? 1u : 0u);
+    }
+    cp_async_commit();
+    (void)blk;
+    return true;
+}
+
+// Producer side (one lane of the dedicated producer warp).  `upto` blocks are issued, each after its
+// stage was released by every consumer warp.  The producer never decodes, so consumers are never
+// held back by a slow sibling: they only ever wait for data.
+template <int SPAN>
+__device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uint32_t blk, uint32_t& p_next,
+                                             uint32_t& p_rr, uint32_t& p_cc, uint32_t upto) {
+    bool ok = true;
+    for (; p_next < upto && ok; ++p_next) ok = producer_issue<SPAN>(sm, it, blk + p_next, p_next, p_rr, p_cc);
+    return ok;
+}
+
+template <int L, int THREADS, int CH, bool ESC>
+__device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st,
+                                           uint32_t& blk) {
+    constexpr int RP = ESC ? 1 : ((32 - L) / L + 1);
+    constexpr uint32_t SPAN = THREADS * CH;
+    static_assert(kSteps % RP == 0, "a block of steps must hold whole windows");
+    using CT = typename Ctx<CH>::T;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t tbl = smem_u32(sm.tbl);
+    const uint32_t ring0 = smem_u32(sm.bitring) + tid * 32u;
+    const uint32_t ctx0 = smem_u32(sm.ctxring) + tid * CH;
+    const uint32_t t0 = it.t_begin + tid * CH;
+
+    // first units of every sub-stream (their chunks were requested in stream_begin)
+    cp_async_wait<0>();
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const uint32_t ring = ring0 + c * THREADS * 32;
+        const uint32_t u = st.ch[c].pos >> 5;
+        st.ch[c].w0 = lds_ordered(ring_unit_addr(ring, u));
+        st.ch[c].w1 = lds_ordered(ring_unit_addr(ring, u + 1));
+        const uint32_t ofs = ((u + 1) << 2) + 16u;
+        cp_async_16_if(ring + (ofs & 16u), it.bo.base + ofs, ((((u + 1) & 3u) == 0u) && ofs + 16u <= it.bo.bytes) ? 1u : 0u);
+    }
+    cp_async_commit();
+
+    uint32_t hi[CH], acc[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) acc[c] = 0;
+    uint32_t c_rr = 0, c_cc = 0, c_base = (uint32_t)sm.rowbase[0];
+    const uint32_t nblocks = (it.nsteps + kSteps - 1) / kSteps;
+    bool ok = true;
+
+    for (uint32_t jb = 0; jb < nblocks; ++jb) {
+        const uint32_t g = blk + jb, stage = g % kStages, round = g / kStages;
+        if (!mbar_wait(smem_u32(&sm.full_bar[stage]), round & 1u)) { ok = false; break; }
+        const uint32_t left = it.nsteps - jb * kSteps;
+        const uint32_t count = left < (uint32_t)kSteps ? left : (uint32_t)kSteps;
+        CT val[kSteps];
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) val[u] = lds_ctx<CH>(ctx0 + (stage * kSteps + u) * SPAN);
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u) {
+            if ((uint32_t)u < count) {
+                if (u % RP == 0) {
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) {
+#ifdef MPS_DBG_NOWIN
+                        hi[c] = st.ch[c].w0 + acc[c];
+#else
+                        hi[c] = schain_window(st.ch[c], ring0 + c * THREADS * 32, it.bo, acc[c] & 0xFFFFu);
+#endif
+                        acc[c] = 0;
+                    }
+                }
+                uint32_t e[CH];
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                    const uint32_t idx = __funnelshift_l(hi[c], ctx_of<L>(Ctx<CH>::byte(val[u], c)), L);
+                    e[c] = lds_table(tbl + (idx << 2));
+                    if constexpr (!ESC) {
+#ifdef MPS_DBG_FIXEDLEN
+                        hi[c] = __funnelshift_l(0u, hi[c], 4u);
+#else
+                        hi[c] = __funnelshift_l(0u, hi[c], e[c]);
+#endif
+                        acc[c] += e[c];
+                    } else {
+                        uint32_t used = e[c] & 0xFu;
+                        if (e[c] & kEscBit) {
+                            e[c] = __funnelshift_l(0u, hi[c], used) & 0xFFFF0000u;
+                            used += 16;
+                        }
+                        acc[c] = used;
+                    }
+                }
+#ifdef MPS_DBG_NOSTORE
+                if (e[0] == 0x12345678u) store_syms<CH>(it.out + (c_base + c_cc + t0), e);
+#else
+                store_syms<CH>(it.out + (c_base + c_cc + t0), e);
+#endif
+                c_cc += it.k_eff;
+                if (c_cc >= it.col_len) { c_cc = 0; ++c_rr; c_base = (uint32_t)sm.rowbase[c_rr < kRowCap ? c_rr : 0]; }
+                if (ESC || (u % RP == RP - 1)) {  // one (possibly empty) group per window block
+                    cp_async_commit();
+                    cp_async_wait<kBitLag>();
+                }
+            }
+        }
+        __syncwarp();
+        if ((tid & 31u) == 0) mbar_arrive(smem_u32(&sm.empty_bar[stage]));
+    }
+    cp_async_wait<0>();
+    blk += nblocks;
+    return ok;
+}
+
 // One symbol with the register bit window (generic path).  Returns the 16-bit symbol.
 template <int L>
 __device__ __forceinline__ uint32_t decode_one_win(BitWin& w, const uint32_t* __restrict__ tbl, uint32_t ctx) {
@@ -313,74 +621,113 @@ __device__ void decode_generic(const Smem& sm, const mps_bucket_tensor& T, int m
 }
 
 // Fuse the bucket's tables into shared memory; returns whether any entry is an ESC.
+// The raw tables of a bucket (up to 80 KB) usually come straight from HBM, so every thread first
+// issues a whole batch of independent 16-byte + 4-byte loads and only then converts them: the batch,
+// not a single load, is what waits for memory.
 template <int L, int THREADS>
 __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& T, int tid) {
     constexpr int TS = 1 << L;                 // entries per table
     constexpr int GROUPS_PER_CTX = TS / 8;     // 8 entries per thread-iteration
     constexpr int NGROUPS = kTableEntries / 8;
+    constexpr int ITERS = NGROUPS / THREADS;
+    constexpr int BATCH = (THREADS >= 512) ? 4 : (ITERS < 8 ? ITERS : 8);  // loads in flight per thread
+    static_assert(NGROUPS % THREADS == 0 && ITERS % BATCH == 0, "table groups must split evenly");
     const bool aligned = ((reinterpret_cast<uintptr_t>(T.decode_syms) & 15u) == 0) &&
                          ((reinterpret_cast<uintptr_t>(T.decode_lens) & 3u) == 0);
     bool esc = false;
-    for (int g = tid; g < NGROUPS; g += THREADS) {
-        const int ctx = g / GROUPS_PER_CTX;
-        const int j0 = (g - ctx * GROUPS_PER_CTX) * 8;
-        const int32_t gid = sm.gid[ctx];
-        uint32_t ent[8];
-        if (gid >= 0) {
-            uint32_t s[4], ln;
-            const uint16_t* sp = T.decode_syms + (long long)gid * TS + j0;
-            const uint8_t* lp = T.decode_lens + (long long)gid * (TS / 2) + (j0 >> 1);
-            if (aligned) {
-                const uint4 v = __ldg(reinterpret_cast<const uint4*>(sp));
-                s[0] = v.x; s[1] = v.y; s[2] = v.z; s[3] = v.w;
-                ln = __ldg(reinterpret_cast<const uint32_t*>(lp));
-            } else {
+    for (int it0 = 0; it0 < ITERS && tid < THREADS; it0 += BATCH) {
+        uint4 sv[BATCH];
+        uint32_t lv[BATCH];
+        int32_t gv[BATCH];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) s[i] = (uint32_t)sp[2 * i] | ((uint32_t)sp[2 * i + 1] << 16);
-                ln = (uint32_t)lp[0] | ((uint32_t)lp[1] << 8) | ((uint32_t)lp[2] << 16) | ((uint32_t)lp[3] << 24);
+        for (int q = 0; q < BATCH; ++q) {
+            const int g = tid + (it0 + q) * THREADS;
+            const int ctx = g / GROUPS_PER_CTX;
+            const int j0 = (g - ctx * GROUPS_PER_CTX) * 8;
+            const int32_t gid = sm.gid[ctx];
+            gv[q] = gid;
+            sv[q] = make_uint4(0u, 0u, 0u, 0u);
+            lv[q] = 0u;
+            if (gid >= 0) {
+                const uint16_t* sp = T.decode_syms + (long long)gid * TS + j0;
+                const uint8_t* lp = T.decode_lens + (long long)gid * (TS / 2) + (j0 >> 1);
+                if (aligned) {
+                    sv[q] = __ldg(reinterpret_cast<const uint4*>(sp));
+                    lv[q] = __ldg(reinterpret_cast<const uint32_t*>(lp));
+                } else {
+                    sv[q].x = (uint32_t)sp[0] | ((uint32_t)sp[1] << 16);
+                    sv[q].y = (uint32_t)sp[2] | ((uint32_t)sp[3] << 16);
+                    sv[q].z = (uint32_t)sp[4] | ((uint32_t)sp[5] << 16);
+                    sv[q].w = (uint32_t)sp[6] | ((uint32_t)sp[7] << 16);
+                    lv[q] = (uint32_t)lp[0] | ((uint32_t)lp[1] << 8) | ((uint32_t)lp[2] << 16) | ((uint32_t)lp[3] << 24);
+                }
             }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t sym = (s[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
-                const uint32_t nib = (ln >> (4 * i)) & 0xFu;
-                uint32_t len, e;
-                if constexpr (L == 7) { len = nib & 7u; e = nib >> 3; }   // bit 3 = ESC, low 3 bits = code length
-                else { e = (nib == 15u); len = e ? (uint32_t)L : nib; }    // nibble 15 = ESC with an L-bit code
-                esc |= (e != 0);
-                ent[i] = (sym << 16) | (e << 15) | len;
-            }
-        } else {
-            // no table for this context: the FP8 decoder emits zeros and consumes nothing
-            // (decode_huffman.cu:252-264); the AWQ decoders treat it as an ESC (:476-485).
-            const uint32_t fill = (L == 7) ? 0u : ((uint32_t)L | kEscBit);
-            esc |= (L != 7);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ent[i] = fill;
         }
-        uint4* dst = reinterpret_cast<uint4*>(&sm.tbl[ctx * TS + j0]);
-        dst[0] = make_uint4(ent[0], ent[1], ent[2], ent[3]);
-        dst[1] = make_uint4(ent[4], ent[5], ent[6], ent[7]);
+#pragma unroll
+        for (int q = 0; q < BATCH; ++q) {
+            const int g = tid + (it0 + q) * THREADS;
+            const int ctx = g / GROUPS_PER_CTX;
+            const int j0 = (g - ctx * GROUPS_PER_CTX) * 8;
+            const uint32_t s[4] = {sv[q].x, sv[q].y, sv[q].z, sv[q].w};
+            uint32_t ent[8];
+            if (gv[q] >= 0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t sym = (s[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+                    const uint32_t nib = (lv[q] >> (4 * i)) & 0xFu;
+                    uint32_t len, e;
+                    if constexpr (L == 7) { len = nib & 7u; e = nib >> 3; }   // bit 3 = ESC, low 3 bits = code length
+                    else { e = (nib == 15u); len = e ? (uint32_t)L : nib; }    // nibble 15 = ESC with an L-bit code
+                    esc |= (e != 0);
+                    ent[i] = (sym << 16) | (e << 15) | len;
+                }
+            } else {
+                // no table for this context: the FP8 decoder emits zeros and consumes nothing
+                // (decode_huffman.cu:252-264); the AWQ decoders treat it as an ESC (:476-485).
+                const uint32_t fill = (L == 7) ? 0u : ((uint32_t)L | kEscBit);
+                esc |= (L != 7);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ent[i] = fill;
+            }
+            uint4* dst = reinterpret_cast<uint4*>(&sm.tbl[ctx * TS + j0]);
+            dst[0] = make_uint4(ent[0], ent[1], ent[2], ent[3]);
+            dst[1] = make_uint4(ent[4], ent[5], ent[6], ent[7]);
+        }
     }
     return __syncthreads_or(esc ? 1 : 0) != 0;
 }
 
 template <int L, int THREADS, int CH>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS + 32, 1)
 bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __restrict__ ws) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
     constexpr int NCTX = (L == 7) ? 256 : 16;
     constexpr uint32_t SPAN = THREADS * CH;  // sub-streams per work item
+    constexpr int NT = THREADS + 32;         // THREADS decoding threads + one producer warp
     const int tid = threadIdx.x;
+    const bool is_consumer = tid < THREADS;
+    const bool is_producer = tid == THREADS;  // first lane of the extra warp
 
     const bool prefix_cached = args.tensors != nullptr && args.count <= kPrefixCap;
     if (prefix_cached)
-        for (int i = tid; i <= args.count; i += THREADS) sm.prefix[i] = args.item_prefix[i];
-    if (tid == 0) sm.staged_tensor = -1;
+        for (int i = tid; i <= args.count; i += NT) sm.prefix[i] = args.item_prefix[i];
+    if (tid == 0) {
+        sm.staged_tensor = -1;
+        sm.abort = 0;
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(smem_u32(&sm.full_bar[i]), 1u);
+            mbar_init(smem_u32(&sm.empty_bar[i]), THREADS / 32);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
     __syncthreads();
 
     bool staged_esc = false;
+    uint32_t blk = 0;  // blocks of steps streamed so far by this CTA (same value in every thread)
     for (;;) {
+        MPS_T0();
         if (tid == 0) sm.item = (int)atomicAdd(&ws[0], 1u);
         __syncthreads();
         const int item = sm.item;
@@ -422,36 +769,11 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         const uint32_t t_begin = chunk * SPAN;
         if (!ok || t_begin >= k_eff) { __syncthreads(); continue; }  // uniform across the CTA
 
-        // ---- tables: restage only when the context->table map changed ----------------------------
-        constexpr int CPT = (NCTX + THREADS - 1) / THREADS;  // contexts per thread
-        int differs = (sm.staged_tensor != ti);
-        int32_t my_gid[CPT];
-#pragma unroll
-        for (int i = 0; i < CPT; ++i) {
-            const int c = tid + i * THREADS;
-            my_gid[i] = -1;
-            if (c < NCTX) {
-                my_gid[i] = T.bucket_table[b * NCTX + c];
-                if (my_gid[i] >= T.num_tables) my_gid[i] = -1;
-                differs |= (my_gid[i] != sm.gid[c]);
-            }
-        }
-        differs = __syncthreads_or(differs);
-        if (differs) {
-#pragma unroll
-            for (int i = 0; i < CPT; ++i) {
-                const int c = tid + i * THREADS;
-                if (c < NCTX) sm.gid[c] = my_gid[i];
-            }
-            if (tid == 0) sm.staged_tensor = ti;
-            __syncthreads();
-            staged_esc = stage_tables<L, THREADS>(sm, T, tid);
-        }
-
+        MPS_TICK(0);  // item fetch + geometry
         // ---- row bases (element offset of each row / group start) ----------------------------------
-        int rows_ok = 1, rows_vec = 1;
+        int rows_ok = 1, rows_vec = 1, rows_al16 = 1;
         const long long ncache = nrows < kRowCap ? nrows : kRowCap;
-        for (long long i = tid; i < ncache; i += THREADS) {
+        for (long long i = tid; i < ncache; i += NT) {
             const long long row = T.row_indices[row_a + i];
             const long long c0 = (mode == 2) ? (long long)T.group_col_start[row_a + i] : col_start;
             const bool good = row >= 0 && row < T.n && c0 >= 0 && c0 + col_len <= T.m;
@@ -459,9 +781,11 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             sm.rowbase[i] = good ? base : -1;
             rows_ok &= good;
             rows_vec &= ((base & (CH - 1)) == 0);
+            rows_al16 &= ((base & 15) == 0);
         }
         rows_ok = __syncthreads_and(rows_ok);
         rows_vec = __syncthreads_and(rows_vec);
+        rows_al16 = __syncthreads_and(rows_al16);
 
         const uint32_t* bs32 = reinterpret_cast<const uint32_t*>(T.bitstream) + 2 * wb;
         const long long units = 2 * (T.bitstream_words - wb);
@@ -472,8 +796,80 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                          (col_len % CH) == 0 && T.n * T.m <= 0xFFFFFFFFLL &&
                          ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & (CH - 1)) == 0) &&
                          ((reinterpret_cast<uintptr_t>(T.out) & (2 * CH - 1)) == 0);
+
+        // ---- streaming path: start the asynchronous copies before the tables are staged ----------------
+        StreamItem it;
+        StreamThread<L, THREADS, CH> st;
+        bool stream = false;
+        if (vec && rows_al16 && t_begin + SPAN <= k_eff && (col_len % k_eff) == 0 && (k_eff % 16u) == 0 &&
+            ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & 15u) == 0) && !MPS_NO_STREAM) {
+            const uint8_t* bucket_bytes = reinterpret_cast<const uint8_t*>(T.bitstream) + 8 * wb;
+            const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(bucket_bytes) & 15u);  // 0 or 8
+            const long long valid = 8 * (T.bitstream_words - wb) + mis;
+            const long long bits = (long long)startbit[k_eff] + 8 * mis;  // end of the bucket's bits from the origin
+            if ((mis == 0u || wb > 0) && valid <= 0x7FFFFFF0LL && (bits >> 3) + 64 <= valid) {
+                stream = true;
+                it.ctx_bytes = T.ctx_bytes; it.out = T.out; it.startbit = startbit;
+                it.bo.base = bucket_bytes - mis; it.bo.bytes = (uint32_t)valid; it.bo.bit_delta = 8 * mis;
+                it.t_begin = t_begin; it.k_eff = k_eff; it.col_len = (uint32_t)col_len;
+                it.nsteps = (uint32_t)(total / k_eff);
+            }
+        }
+        MPS_TICK(1);  // row bases
+        bool run_ok = true;
+        uint32_t p_next = 0, p_rr = 0, p_cc = 0, nblocks = 0;
+        if (stream) {
+            nblocks = (it.nsteps + kSteps - 1) / kSteps;
+            if (is_consumer) run_ok = stream_begin<L, THREADS, CH>(sm, it, st, blk);
+            else if (is_producer)  // every stage is free at the start of an item: no waiting here
+                run_ok = producer_run<SPAN>(sm, it, blk, p_next, p_rr, p_cc, nblocks < (uint32_t)kStages ? nblocks : kStages);
+        }
+        MPS_TICK(2);  // async copies started
+
+        // ---- tables: restage only when the context->table map changed ----------------------------
+        constexpr int CPT = (NCTX + THREADS - 1) / THREADS;  // contexts per thread
+        int differs = (sm.staged_tensor != ti);
+        int32_t my_gid[CPT];
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            const int c = tid + i * THREADS;
+            my_gid[i] = -1;
+            if (is_consumer && c < NCTX) {
+                my_gid[i] = T.bucket_table[b * NCTX + c];
+                if (my_gid[i] >= T.num_tables) my_gid[i] = -1;
+                differs |= (my_gid[i] != sm.gid[c]);
+            }
+        }
+        differs = __syncthreads_or(differs);
+        if (differs) {
+#pragma unroll
+            for (int i = 0; i < CPT; ++i) {
+                const int c = tid + i * THREADS;
+                if (is_consumer && c < NCTX) sm.gid[c] = my_gid[i];
+            }
+            if (tid == 0) sm.staged_tensor = ti;
+            __syncthreads();
+            staged_esc = stage_tables<L, THREADS>(sm, T, tid);
+        }
+
+        MPS_TICK(3);  // tables
+        // ---- decode ------------------------------------------------------------------------------
         const uint32_t t0 = t_begin + (uint32_t)tid * CH;
-        if (vec) {
+        if (stream) {
+            if (is_consumer) {
+                uint32_t b2 = blk;
+                if (run_ok) {
+                    run_ok = staged_esc ? stream_run<L, THREADS, CH, true>(sm, it, st, b2)
+                                        : stream_run<L, THREADS, CH, false>(sm, it, st, b2);
+                }
+            } else if (is_producer && run_ok) {
+                run_ok = producer_run<SPAN>(sm, it, blk, p_next, p_rr, p_cc, nblocks);
+            }
+            if (!run_ok) sm.abort = 1;
+            blk += nblocks;
+        } else if (!is_consumer) {
+            // the producer warp has nothing to do on the non-streaming paths
+        } else if (vec) {
             if (t0 < k_eff) {
                 if (staged_esc)
                     decode_vec<L, CH, true>(sm, T.ctx_bytes, T.out, bs32, lim, startbit, t0, k_eff, (uint32_t)col_len,
@@ -486,7 +882,13 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             const uint32_t t1 = (t0 + CH < k_eff) ? t0 + CH : k_eff;
             decode_generic<L>(sm, T, mode, bs32, lim, startbit, t0, t1, k_eff, col_len, col_start, row_a, total);
         }
+        MPS_TICK(stream ? 4 : 5);  // decode (streaming / other paths), thread 0's own share
         __syncthreads();  // everyone is done with tbl / rowbase / item before they are overwritten
+        MPS_TICK(6);  // waiting for the slowest warp
+        if (sm.abort) {   // a bounded wait ran out: report and stop taking work (uniform: read after the barrier)
+            if (tid == 0) atomicOr(&ws[2], 1u);
+            break;
+        }
     }
 
     // last CTA out re-zeroes the queue so the next launch on this stream can reuse the workspace
@@ -530,7 +932,7 @@ static int launch_cfg(const BatchArgs& a, unsigned int* ws, cudaStream_t st) {
     int grid = sm_count();
     if (a.total_items < grid) grid = a.total_items;
     if (grid <= 0) return MPS_OK;
-    bucket_decode_kernel<L, THREADS, CH><<<grid, THREADS, smem, st>>>(a, ws);
+    bucket_decode_kernel<L, THREADS, CH><<<grid, THREADS + 32, smem, st>>>(a, ws);
     MPS_CUDA_TRY(cudaGetLastError());
     return MPS_OK;
 }
@@ -538,7 +940,6 @@ static int launch_cfg(const BatchArgs& a, unsigned int* ws, cudaStream_t st) {
 template <int L>
 static int launch_L(const BatchArgs& a, int threads, int chains, unsigned int* ws, cudaStream_t st) {
 #define MPS_CASE(T_, C_) if (threads == T_ && chains == C_) return launch_cfg<L, T_, C_>(a, ws, st)
-    MPS_CASE(1024, 1);
     MPS_CASE(512, 2);
     MPS_CASE(512, 1);
     MPS_CASE(256, 4);
