@@ -52,8 +52,9 @@ int cuda_fail(cudaError_t e, const char* what) {
 // ------------------------------------------------------------------------------------------------
 constexpr int kTableEntries = 32768;  // 256 ctx x 2^7 == 16 ctx x 2^11
 constexpr int kRowCap = 1024;         // rows / groups of a bucket cached in shared memory
-constexpr int kPrefixCap = 512;       // tensors of a batch whose item prefix is cached in shared memory
-constexpr int kSteps = 4;             // steps per software-pipeline block
+constexpr int kPrefixCap = 128;       // tensors of a batch whose item prefix is cached in shared memory
+constexpr int kSteps = 4;             // steps per software-pipeline block (register-prefetch path)
+constexpr int kSS = 8;                // steps per stage of the streaming path's context ring
 #ifndef MPS_LOOK
 #define MPS_LOOK 1
 #endif
@@ -71,16 +72,16 @@ struct BatchArgs {
 };
 
 #ifndef MPS_STAGES
-#define MPS_STAGES 8
+#define MPS_STAGES 3
 #endif
 constexpr int kStages = MPS_STAGES;            // context-byte ring: stages of kSteps steps each
 constexpr int kMaxSpan = 1024;        // sub-streams per work item (threads x chains), at most
 
 struct Smem {
     uint32_t tbl[kTableEntries];                 // fused entries: sym << 16 | esc << 15 | code length
-    uint4 bitring[2 * kMaxSpan];                 // per sub-stream: two 16-byte halves of its bitstream
-    uint8_t ctxring[kStages * kSteps * kMaxSpan];  // context bytes of the next kStages blocks of steps
-    long long rowbase[kRowCap];
+    uint4 bitring[4 * kMaxSpan];                 // per sub-stream: four 16-byte chunks of its bitstream
+    uint8_t ctxring[kStages * kSS * kMaxSpan];   // context bytes of the next kStages blocks of steps
+    uint32_t rowbase[kRowCap];                   // element offset of each row / group start (0xFFFFFFFF: invalid)
     long long prefix[kPrefixCap + 1];
     unsigned long long full_bar[kStages];        // bulk copies of a stage have landed
     unsigned long long empty_bar[kStages];       // every warp is done reading a stage
@@ -374,31 +375,52 @@ __device__ __forceinline__ void lds_ordered_if(uint32_t& v, uint32_t addr, uint3
 
 struct BitOrigin {        // bitstream of the item seen from a 16-byte aligned origin
     const uint8_t* base;  // 16-byte aligned
-    uint32_t bytes;       // valid bytes from base
+    uint32_t last_ofs;    // largest 16-byte aligned offset whose chunk lies wholly inside the bitstream
     uint32_t bit_delta;   // bits between the origin and the bucket's first bit (0 or 64)
 };
 
-// 32-bit unit x (bit order) of the stream sits at byte 4*(x^1); the ring keeps byte offsets mod 32.
-__device__ __forceinline__ uint32_t ring_unit_addr(uint32_t ring, uint32_t x) { return ring + (((x ^ 1u) & 7u) << 2); }
+constexpr int kRingChunks = 4;                        // 16-byte chunks of bitstream kept per sub-stream
+constexpr uint32_t kRingBytes = 16u * kRingChunks;    // 64
+
+// 32-bit unit x (bit order) of the stream sits at byte 4*(x^1); the ring keeps byte offsets mod 64.
+__device__ __forceinline__ uint32_t ring_unit_addr(uint32_t ring, uint32_t x) {
+    return ring + (((x ^ 1u) & (kRingBytes / 4 - 1)) << 2);
+}
 
 struct SChain {
     uint32_t pos;     // bit position relative to BitOrigin::base
     uint32_t w0, w1;  // units pos>>5 and (pos>>5)+1
+    uint32_t next;    // next 16-byte chunk to request
 };
 
-// Move by `used` (< 32) bits; returns the fresh 32-bit window.  When w1 becomes the first unit of
-// a 16-byte chunk, the copy of the following chunk is started (predicated, no branch).
-__device__ __forceinline__ uint32_t schain_window(SChain& ch, uint32_t ring, const BitOrigin& bo, uint32_t used) {
+// Move by `used` (< 32) bits and return the fresh 32-bit window.  Branch-free: the register
+// rotation and the ring read are predicated on having moved into the next unit.
+__device__ __forceinline__ uint32_t schain_window(SChain& ch, uint32_t ring, uint32_t used) {
     const uint32_t np = ch.pos + used;
-    const uint32_t cross = ((np ^ ch.pos) > 31u) ? 1u : 0u;
-    const uint32_t x = (np >> 5) + 1;  // unit that w1 must hold
+    const uint32_t moved = np ^ ch.pos;
+    const uint32_t addr = ring_unit_addr(ring, (np >> 5) + 1);
     ch.pos = np;
-    ch.w0 = cross ? ch.w1 : ch.w0;
-    lds_ordered_if(ch.w1, ring_unit_addr(ring, x), cross);
-    const uint32_t ofs = (x << 2) + 16u;  // byte offset of the chunk after x's, valid when x % 4 == 0
-    const uint32_t fetch = (cross && (x & 3u) == 0u && ofs + 16u <= bo.bytes) ? 1u : 0u;
-    cp_async_16_if(ring + (ofs & 16u), bo.base + ofs, fetch);
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.gt.u32 p, %2, 31;\n\t@p mov.u32 %0, %1;\n\t@p ld.shared.u32 %1, [%3];\n\t}"
+        : "+r"(ch.w0), "+r"(ch.w1)
+        : "r"(moved), "r"(addr)
+        : "memory");
     return __funnelshift_l(ch.w1, ch.w0, np);
+}
+
+// Keep kRingChunks chunks requested from the one w1 sits in: at most one new request per call,
+// which is enough as long as fewer than 128 bits are consumed between calls.  Chunk c lives in ring
+// slot c % kRingChunks; slot reuse is safe because chunk c - kRingChunks lies wholly before w0.
+__device__ __forceinline__ void schain_request(SChain& ch, uint32_t ring, const BitOrigin& bo) {
+    const uint32_t need = (((ch.pos >> 5) + 1) >> 2) + kRingChunks;  // chunks below `need` must be on their way
+    const uint32_t ofs = ch.next << 4;
+    const uint8_t* src = bo.base + min(ofs, bo.last_ofs);           // clamped: never outside the bitstream
+    const uint32_t dst = ring + (ofs & (kRingBytes - 1));
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %0, %1;\n\t@p cp.async.cg.shared.global [%2], [%3], 16;\n\t@p add.u32 %0, %0, 1;\n\t}"
+        : "+r"(ch.next)
+        : "r"(need), "r"(dst), "l"(src)
+        : "memory");
 }
 
 template <int CH>
@@ -425,49 +447,22 @@ struct StreamItem {
     uint32_t t_begin, k_eff, col_len, nsteps;
 };
 
-// Copies of block `jb` of the item (elected thread only).  Returns false if the stage never freed.
+// Copies of block `jb` of the item (producer lane only).  Returns false if the stage never freed.
 template <int SPAN>
 __device__ __forceinline__ bool producer_issue(Smem& sm, const StreamItem& it, uint32_t g, uint32_t jb, uint32_t& p_rr,
                                                uint32_t& p_cc) {
     const uint32_t stage = g % kStages, round = g / kStages;
     const uint32_t full = smem_u32(&sm.full_bar[stage]);
     if (!mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u)) return false;
-    const uint32_t left = it.nsteps - jb * kSteps;
-    const uint32_t nst = left < (uint32_t)kSteps ? left : (uint32_t)kSteps;
+    const uint32_t left = it.nsteps - jb * kSS;
+    const uint32_t nst = left < (uint32_t)kSS ? left : (uint32_t)kSS;
     mbar_expect_tx(full, nst * SPAN);
     for (uint32_t u = 0; u < nst; ++u) {
         const uint8_t* src = it.ctx_bytes + (uint32_t)sm.rowbase[p_rr] + p_cc + it.t_begin;
-        bulk_g2s(smem_u32(sm.ctxring) + (stage * kSteps + u) * SPAN, src, SPAN, full);
+        bulk_g2s(smem_u32(sm.ctxring) + (stage * kSS + u) * SPAN, src, SPAN, full);
         p_cc += it.k_eff;
         if (p_cc >= it.col_len) { p_cc = 0; ++p_rr; }
     }
-    return true;
-}
-
-template <int L, int THREADS, int CH>
-struct StreamThread {  // per-thread state that lives from stream_begin to stream_run
-    SChain ch[CH];
-};
-
-// Start everything that can overlap with table staging: first bitstream chunks of every
-// sub-stream, first kStages blocks of context bytes.
-template <int L, int THREADS, int CH>
-__device__ __forceinline__ bool stream_begin(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st,
-                                             uint32_t blk) {
-    constexpr uint32_t SPAN = THREADS * CH;
-    const uint32_t tid = threadIdx.x;
-    const uint32_t ring0 = smem_u32(sm.bitring) + tid * 32u;
-#pragma unroll
-    for (int c = 0; c < CH; ++c) {
-        const uint32_t ring = ring0 + c * THREADS * 32;
-        const uint32_t pos = it.startbit[it.t_begin + tid * CH + c] + it.bo.bit_delta;
-        st.ch[c].pos = pos;
-        const uint32_t o0 = (pos >> 7) << 4, o1 = o0 + 16u;
-        cp_async_16_if(ring + (o0 & 16u), it.bo.base + o0, (o0 + 16u <= it.bo.bytes) ? 1u : 0u);
-        cp_async_16_if(ring + (o1 & 16u), it.bo.base + o1, (o1 + 16u <= it.bo.bytes) ? 1u : 0u);
-    }
-    cp_async_commit();
-    (void)blk;
     return true;
 }
 
@@ -482,16 +477,50 @@ __device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uin
     return ok;
 }
 
+template <int L, int THREADS, int CH>
+struct StreamThread {  // per-thread state that lives from stream_begin to stream_run
+    SChain ch[CH];
+};
+
+// Start what can overlap with table staging: the first chunks of every sub-stream's bitstream.
+template <int L, int THREADS, int CH>
+__device__ __forceinline__ void stream_begin(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st) {
+    const uint32_t tid = threadIdx.x;
+    const uint32_t ring0 = smem_u32(sm.bitring) + tid * kRingBytes;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        const uint32_t ring = ring0 + c * THREADS * kRingBytes;
+        const uint32_t pos = it.startbit[it.t_begin + tid * CH + c] + it.bo.bit_delta;
+        st.ch[c].pos = pos;
+        const uint32_t c0 = pos >> 7;
+#pragma unroll
+        for (int q = 0; q < kRingChunks; ++q) {
+            const uint32_t ofs = (c0 + q) << 4;
+            cp_async_16(ring + (ofs & (kRingBytes - 1)), it.bo.base + min(ofs, it.bo.last_ofs));
+        }
+        st.ch[c].next = c0 + kRingChunks;
+    }
+    cp_async_commit();
+}
+
 template <int L, int THREADS, int CH, bool ESC>
 __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st,
-                                           uint32_t& blk) {
-    constexpr int RP = ESC ? 1 : ((32 - L) / L + 1);
+                                           uint32_t blk) {
+    constexpr int RP = ESC ? 1 : ((32 - L) / L + 1);   // symbols per 32-bit window
+    constexpr int CHK = ESC ? 4 : kSS;                   // steps between bitstream requests
+    constexpr int MAXBITS = ESC ? (L + 16) : L;          // most bits one step can consume
+    static_assert(CHK * MAXBITS < 128, "at most one chunk boundary between two requests");
+    // A chunk requested when w1 enters chunk k is first read when w1 enters chunk k + kRingChunks - 1,
+    // at least NEED steps later; requests are committed every CHK steps and cp.async.wait_group LAG
+    // then guarantees everything committed LAG commits ago, so LAG = NEED / CHK - 2 is always safe.
+    constexpr int NEED = ((kRingChunks - 1) * 128 + MAXBITS - 1) / MAXBITS;
+    constexpr int LAG = (NEED / CHK - 2) > 0 ? (NEED / CHK - 2) : 0;
     constexpr uint32_t SPAN = THREADS * CH;
-    static_assert(kSteps % RP == 0, "a block of steps must hold whole windows");
+    static_assert(kSS % RP == 0 && kSS % CHK == 0, "a stage must hold whole windows and request periods");
     using CT = typename Ctx<CH>::T;
     const uint32_t tid = threadIdx.x;
     const uint32_t tbl = smem_u32(sm.tbl);
-    const uint32_t ring0 = smem_u32(sm.bitring) + tid * 32u;
+    const uint32_t ring0 = smem_u32(sm.bitring) + tid * kRingBytes;
     const uint32_t ctx0 = smem_u32(sm.ctxring) + tid * CH;
     const uint32_t t0 = it.t_begin + tid * CH;
 
@@ -499,75 +528,70 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
     cp_async_wait<0>();
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-        const uint32_t ring = ring0 + c * THREADS * 32;
+        const uint32_t ring = ring0 + c * THREADS * kRingBytes;
         const uint32_t u = st.ch[c].pos >> 5;
         st.ch[c].w0 = lds_ordered(ring_unit_addr(ring, u));
         st.ch[c].w1 = lds_ordered(ring_unit_addr(ring, u + 1));
-        const uint32_t ofs = ((u + 1) << 2) + 16u;
-        cp_async_16_if(ring + (ofs & 16u), it.bo.base + ofs, ((((u + 1) & 3u) == 0u) && ofs + 16u <= it.bo.bytes) ? 1u : 0u);
     }
-    cp_async_commit();
 
     uint32_t hi[CH], acc[CH];
 #pragma unroll
     for (int c = 0; c < CH; ++c) acc[c] = 0;
-    uint32_t c_rr = 0, c_cc = 0, c_base = (uint32_t)sm.rowbase[0];
-    const uint32_t nblocks = (it.nsteps + kSteps - 1) / kSteps;
-    bool ok = true;
+    uint32_t c_rr = 0, c_cc = 0;
+    uint16_t* outp = it.out + ((uint32_t)sm.rowbase[0] + t0);
+    const uint32_t nblocks = (it.nsteps + kSS - 1) / kSS;
 
     for (uint32_t jb = 0; jb < nblocks; ++jb) {
         const uint32_t g = blk + jb, stage = g % kStages, round = g / kStages;
-        if (!mbar_wait(smem_u32(&sm.full_bar[stage]), round & 1u)) { ok = false; break; }
-        const uint32_t left = it.nsteps - jb * kSteps;
-        const uint32_t count = left < (uint32_t)kSteps ? left : (uint32_t)kSteps;
-        CT val[kSteps];
+        if (!mbar_wait(smem_u32(&sm.full_bar[stage]), round & 1u)) return false;
+        const uint32_t left = it.nsteps - jb * kSS;
+        const uint32_t count = left < (uint32_t)kSS ? left : (uint32_t)kSS;
+        CT val[kSS];
 #pragma unroll
-        for (int u = 0; u < kSteps; ++u) val[u] = lds_ctx<CH>(ctx0 + (stage * kSteps + u) * SPAN);
+        for (int u = 0; u < kSS; ++u) val[u] = lds_ctx<CH>(ctx0 + (stage * kSS + u) * SPAN);
 #pragma unroll
-        for (int u = 0; u < kSteps; ++u) {
-            if ((uint32_t)u < count) {
+        for (int u = 0; u < kSS; ++u) {
+            if ((uint32_t)u < count) {  // uniform; false only in the last block of an item
                 if (u % RP == 0) {
 #pragma unroll
                     for (int c = 0; c < CH; ++c) {
-#ifdef MPS_DBG_NOWIN
-                        hi[c] = st.ch[c].w0 + acc[c];
-#else
-                        hi[c] = schain_window(st.ch[c], ring0 + c * THREADS * 32, it.bo, acc[c] & 0xFFFFu);
-#endif
+                        hi[c] = schain_window(st.ch[c], ring0 + c * THREADS * kRingBytes, acc[c] & 0xFFFFu);
                         acc[c] = 0;
                     }
                 }
                 uint32_t e[CH];
 #pragma unroll
                 for (int c = 0; c < CH; ++c) {
+                    // index = ctx << L | top L bits of the window, in one funnel shift
                     const uint32_t idx = __funnelshift_l(hi[c], ctx_of<L>(Ctx<CH>::byte(val[u], c)), L);
                     e[c] = lds_table(tbl + (idx << 2));
                     if constexpr (!ESC) {
-#ifdef MPS_DBG_FIXEDLEN
-                        hi[c] = __funnelshift_l(0u, hi[c], 4u);
-#else
-                        hi[c] = __funnelshift_l(0u, hi[c], e[c]);
-#endif
-                        acc[c] += e[c];
+                        hi[c] = __funnelshift_l(0u, hi[c], e[c]);  // shift by the low 5 bits = code length
+                        acc[c] += e[c];                            // low half accumulates the lengths
                     } else {
                         uint32_t used = e[c] & 0xFu;
-                        if (e[c] & kEscBit) {
+                        if (e[c] & kEscBit) {                     // 16 raw bits follow the ESC code
                             e[c] = __funnelshift_l(0u, hi[c], used) & 0xFFFF0000u;
                             used += 16;
                         }
                         acc[c] = used;
                     }
                 }
-#ifdef MPS_DBG_NOSTORE
-                if (e[0] == 0x12345678u) store_syms<CH>(it.out + (c_base + c_cc + t0), e);
-#else
-                store_syms<CH>(it.out + (c_base + c_cc + t0), e);
-#endif
+                store_syms<CH>(outp, e);
                 c_cc += it.k_eff;
-                if (c_cc >= it.col_len) { c_cc = 0; ++c_rr; c_base = (uint32_t)sm.rowbase[c_rr < kRowCap ? c_rr : 0]; }
-                if (ESC || (u % RP == RP - 1)) {  // one (possibly empty) group per window block
+                outp += it.k_eff;
+                if (c_cc >= it.col_len) {  // next row of the bucket (uniform)
+                    c_cc = 0;
+                    ++c_rr;
+                    outp = it.out + ((uint32_t)sm.rowbase[c_rr < kRowCap ? c_rr : 0] + t0);
+                }
+                if ((u + 1) % CHK == 0) {
+                    // the position used for the request is the one of the last window; the bits consumed
+                    // since then (< 32) can only make the request one period late, which NEED allows for
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) schain_request(st.ch[c], ring0 + c * THREADS * kRingBytes, it.bo);
                     cp_async_commit();
-                    cp_async_wait<kBitLag>();
+                    cp_async_wait<LAG>();
                 }
             }
         }
@@ -575,8 +599,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
         if ((tid & 31u) == 0) mbar_arrive(smem_u32(&sm.empty_bar[stage]));
     }
     cp_async_wait<0>();
-    blk += nblocks;
-    return ok;
+    return true;
 }
 
 // One symbol with the register bit window (generic path).  Returns the 16-bit symbol.
@@ -598,13 +621,14 @@ __device__ void decode_generic(const Smem& sm, const mps_bucket_tensor& T, int m
                                uint32_t lim, const uint32_t* __restrict__ startbit, uint32_t t_begin, uint32_t t_end,
                                uint32_t k_eff, long long col_len, long long col_start, long long row_a,
                                long long total) {
+    const bool small = T.n * T.m < 0xFFFFFFFFLL;  // cached row bases are 32-bit
     for (uint32_t t = t_begin; t < t_end; ++t) {
         BitWin w;
         win_init(w, bs32, lim, startbit[t]);
         for (long long e = t; e < total; e += k_eff) {
             const long long rr = e / col_len, cc = e - rr * col_len;
             long long base;
-            if (rr < kRowCap) base = sm.rowbase[rr];
+            if (rr < kRowCap && small) base = (sm.rowbase[rr] == 0xFFFFFFFFu) ? -1 : (long long)sm.rowbase[rr];
             else {
                 const long long row = T.row_indices[row_a + rr];
                 const long long c0 = (mode == 2) ? (long long)T.group_col_start[row_a + rr] : col_start;
@@ -778,7 +802,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             const long long c0 = (mode == 2) ? (long long)T.group_col_start[row_a + i] : col_start;
             const bool good = row >= 0 && row < T.n && c0 >= 0 && c0 + col_len <= T.m;
             const long long base = row * T.m + c0;
-            sm.rowbase[i] = good ? base : -1;
+            sm.rowbase[i] = (good && base < 0xFFFFFFFFLL) ? (uint32_t)base : 0xFFFFFFFFu;
             rows_ok &= good;
             rows_vec &= ((base & (CH - 1)) == 0);
             rows_al16 &= ((base & 15) == 0);
@@ -793,7 +817,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         const uint32_t* startbit = T.thread_startbit + b * ((long long)k + 1);
 
         const bool vec = rows_ok && rows_vec && nrows <= kRowCap && (k_eff % CH) == 0 &&
-                         (col_len % CH) == 0 && T.n * T.m <= 0xFFFFFFFFLL &&
+                         (col_len % CH) == 0 && T.n * T.m < 0xFFFFFFFFLL &&
                          ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & (CH - 1)) == 0) &&
                          ((reinterpret_cast<uintptr_t>(T.out) & (2 * CH - 1)) == 0);
 
@@ -807,10 +831,11 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(bucket_bytes) & 15u);  // 0 or 8
             const long long valid = 8 * (T.bitstream_words - wb) + mis;
             const long long bits = (long long)startbit[k_eff] + 8 * mis;  // end of the bucket's bits from the origin
-            if ((mis == 0u || wb > 0) && valid <= 0x7FFFFFF0LL && (bits >> 3) + 64 <= valid) {
+            // every chunk a valid sub-stream can ask for (kRingChunks ahead of its last unit) must exist
+            if ((mis == 0u || wb > 0) && valid <= 0x7FFFFFF0LL && (bits >> 3) + 16 * (kRingChunks + 2) <= valid) {
                 stream = true;
                 it.ctx_bytes = T.ctx_bytes; it.out = T.out; it.startbit = startbit;
-                it.bo.base = bucket_bytes - mis; it.bo.bytes = (uint32_t)valid; it.bo.bit_delta = 8 * mis;
+                it.bo.base = bucket_bytes - mis; it.bo.last_ofs = (uint32_t)((valid - 16) & ~15LL); it.bo.bit_delta = 8 * mis;
                 it.t_begin = t_begin; it.k_eff = k_eff; it.col_len = (uint32_t)col_len;
                 it.nsteps = (uint32_t)(total / k_eff);
             }
@@ -819,8 +844,8 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         bool run_ok = true;
         uint32_t p_next = 0, p_rr = 0, p_cc = 0, nblocks = 0;
         if (stream) {
-            nblocks = (it.nsteps + kSteps - 1) / kSteps;
-            if (is_consumer) run_ok = stream_begin<L, THREADS, CH>(sm, it, st, blk);
+            nblocks = (it.nsteps + kSS - 1) / kSS;
+            if (is_consumer) stream_begin<L, THREADS, CH>(sm, it, st);
             else if (is_producer)  // every stage is free at the start of an item: no waiting here
                 run_ok = producer_run<SPAN>(sm, it, blk, p_next, p_rr, p_cc, nblocks < (uint32_t)kStages ? nblocks : kStages);
         }
@@ -857,11 +882,8 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         const uint32_t t0 = t_begin + (uint32_t)tid * CH;
         if (stream) {
             if (is_consumer) {
-                uint32_t b2 = blk;
-                if (run_ok) {
-                    run_ok = staged_esc ? stream_run<L, THREADS, CH, true>(sm, it, st, b2)
-                                        : stream_run<L, THREADS, CH, false>(sm, it, st, b2);
-                }
+                run_ok = staged_esc ? stream_run<L, THREADS, CH, true>(sm, it, st, blk)
+                                    : stream_run<L, THREADS, CH, false>(sm, it, st, blk);
             } else if (is_producer && run_ok) {
                 run_ok = producer_run<SPAN>(sm, it, blk, p_next, p_rr, p_cc, nblocks);
             }
