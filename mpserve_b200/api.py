@@ -381,11 +381,16 @@ class BucketDecodePlan:
         self.outputs: list[torch.Tensor] = []
         self._keep = []
         descs = (_lib.BucketTensor * len(entries))()
-        for i, (ctx, art, out) in enumerate(entries):
+        outs: list = [None] * len(entries)
+        # widest buckets first: the work queue hands out items in descriptor order, and finishing with
+        # the small items keeps the tail of the launch short
+        order = sorted(range(len(entries)), key=lambda j: (-int(entries[j][0].shape[1]), -int(entries[j][0].shape[0])))
+        for i, j in enumerate(order):
+            ctx, art, out = entries[j]
             n, m = int(ctx.shape[0]), int(ctx.shape[1])
             if out is None:
                 out = torch.empty((n, m), dtype=torch.bfloat16, device=self.device)
-            self.outputs.append(out)
+            outs[j] = out
             self._keep.append((ctx, art))
             d = descs[i]
             d.ctx_bytes = ctx.data_ptr()
@@ -414,6 +419,7 @@ class BucketDecodePlan:
             d.mode = self.mode
             d.n, d.m = n, m
             d.out = out.data_ptr()
+        self.outputs = outs  # in the caller's order
         count = len(entries)
         prefix = (C.c_int64 * (count + 1))()
         threads, chains = C.c_int32(0), C.c_int32(0)

@@ -77,16 +77,43 @@ struct BatchArgs {
 constexpr int kStages = MPS_STAGES;            // context-byte ring: stages of kSteps steps each
 constexpr int kMaxSpan = 1024;        // sub-streams per work item (threads x chains), at most
 
+// ------------------------------------------------------------------------------------------------
+// Work item prepared one item ahead by the scout warp, so that the decoding warps start every item
+// with its geometry and row bases already in shared memory and its tables already on their way
+// into L2 instead of walking a chain of dependent global loads.
+// ------------------------------------------------------------------------------------------------
+struct Prepared {
+    int valid;  // 0: the queue is empty
+    int ok;     // geometry usable, else the item is skipped
+    int ti, mode;
+    uint32_t k, k_eff, t_begin, ebits;
+    long long b, row_a, nrows, col_start, col_len, total, wb;
+    int rows_ok, rows_vec, rows_al16;
+};
+
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// consumer-only barrier (id 1) with an OR reduction
+__device__ __forceinline__ int group_or(int pred, int nthreads) {
+    int r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.s32 p, %1, 0;\n\tbar.red.or.pred q, 1, %2, p;\n\tselp.s32 %0, 1, 0, q;\n\t}"
+        : "=r"(r) : "r"(pred), "r"(nthreads) : "memory");
+    return r;
+}
+__device__ __forceinline__ void group_sync(int nthreads) { asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory"); }
+
 struct Smem {
     uint32_t tbl[kTableEntries];                 // fused entries: sym << 16 | esc << 15 | code length
     uint4 bitring[4 * kMaxSpan];                 // per sub-stream: four 16-byte chunks of its bitstream
     uint8_t ctxring[kStages * kSS * kMaxSpan];   // context bytes of the next kStages blocks of steps
-    uint32_t rowbase[kRowCap];                   // element offset of each row / group start (0xFFFFFFFF: invalid)
+    uint32_t rowbase[2][kRowCap];                // element offset of each row / group start (0xFFFFFFFF: invalid),
+                                                 // one set for the item being decoded, one being prepared
+    Prepared prep[2];
     long long prefix[kPrefixCap + 1];
     unsigned long long full_bar[kStages];        // bulk copies of a stage have landed
     unsigned long long empty_bar[kStages];       // every warp is done reading a stage
     int32_t gid[256];
-    int item;
     int staged_tensor;
     int abort;                                   // a bounded wait gave up
 };
@@ -213,7 +240,7 @@ __device__ __forceinline__ uint32_t chain_window(Chain<LOOK>& ch, const uint32_t
 
 // Vector path: CH adjacent sub-streams per thread, all CH elements of a step contiguous in memory.
 template <int L, int CH, bool ESC>
-__device__ __forceinline__ void decode_vec(const Smem& sm, const uint8_t* __restrict__ ctx_bytes,
+__device__ __forceinline__ void decode_vec(const Smem& sm, const uint32_t* rowbase, const uint8_t* __restrict__ ctx_bytes,
                                            uint16_t* __restrict__ out, const uint32_t* __restrict__ bs32, uint32_t lim,
                                            const uint32_t* __restrict__ startbit, uint32_t t0, uint32_t k_eff,
                                            uint32_t col_len, uint32_t nrows, uint32_t total) {
@@ -231,7 +258,7 @@ __device__ __forceinline__ void decode_vec(const Smem& sm, const uint8_t* __rest
     // (row, col) walk of the prefetcher; division only here, then incremental
     uint32_t p_rr = t0 / col_len;
     uint32_t p_cc = t0 - p_rr * col_len;
-    uint32_t p_base = (uint32_t)sm.rowbase[p_rr];
+    uint32_t p_base = rowbase[p_rr];
     auto fetch = [&](uint32_t s, uint32_t& o, CT& v) {
         if (s < nsteps) {
             o = p_base + p_cc;
@@ -239,7 +266,7 @@ __device__ __forceinline__ void decode_vec(const Smem& sm, const uint8_t* __rest
             p_cc += k_eff;
             if (p_cc >= col_len) {
                 do { p_cc -= col_len; ++p_rr; } while (p_cc >= col_len);
-                p_base = (p_rr < nrows) ? (uint32_t)sm.rowbase[p_rr] : 0u;
+                p_base = (p_rr < nrows) ? rowbase[p_rr] : 0u;
             }
         }
     };
@@ -443,6 +470,7 @@ struct StreamItem {
     const uint8_t* ctx_bytes;
     uint16_t* out;
     const uint32_t* startbit;
+    const uint32_t* rowbase;
     BitOrigin bo;
     uint32_t t_begin, k_eff, col_len, nsteps;
 };
@@ -458,7 +486,7 @@ __device__ __forceinline__ bool producer_issue(Smem& sm, const StreamItem& it, u
     const uint32_t nst = left < (uint32_t)kSS ? left : (uint32_t)kSS;
     mbar_expect_tx(full, nst * SPAN);
     for (uint32_t u = 0; u < nst; ++u) {
-        const uint8_t* src = it.ctx_bytes + (uint32_t)sm.rowbase[p_rr] + p_cc + it.t_begin;
+        const uint8_t* src = it.ctx_bytes + it.rowbase[p_rr < kRowCap ? p_rr : 0] + p_cc + it.t_begin;
         bulk_g2s(smem_u32(sm.ctxring) + (stage * kSS + u) * SPAN, src, SPAN, full);
         p_cc += it.k_eff;
         if (p_cc >= it.col_len) { p_cc = 0; ++p_rr; }
@@ -538,7 +566,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
 #pragma unroll
     for (int c = 0; c < CH; ++c) acc[c] = 0;
     uint32_t c_rr = 0, c_cc = 0;
-    uint16_t* outp = it.out + ((uint32_t)sm.rowbase[0] + t0);
+    uint16_t* outp = it.out + (it.rowbase[0] + t0);
     const uint32_t nblocks = (it.nsteps + kSS - 1) / kSS;
 
     for (uint32_t jb = 0; jb < nblocks; ++jb) {
@@ -583,7 +611,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                 if (c_cc >= it.col_len) {  // next row of the bucket (uniform)
                     c_cc = 0;
                     ++c_rr;
-                    outp = it.out + ((uint32_t)sm.rowbase[c_rr < kRowCap ? c_rr : 0] + t0);
+                    outp = it.out + (it.rowbase[c_rr < kRowCap ? c_rr : 0] + t0);
                 }
                 if ((u + 1) % CHK == 0) {
                     // the position used for the request is the one of the last window; the bits consumed
@@ -617,7 +645,7 @@ __device__ __forceinline__ uint32_t decode_one_win(BitWin& w, const uint32_t* __
 
 // Generic path: any shape and alignment, one element at a time, 64-bit indices, per-element checks.
 template <int L>
-__device__ void decode_generic(const Smem& sm, const mps_bucket_tensor& T, int mode, const uint32_t* __restrict__ bs32,
+__device__ void decode_generic(const Smem& sm, const uint32_t* rowbase, const mps_bucket_tensor& T, int mode, const uint32_t* __restrict__ bs32,
                                uint32_t lim, const uint32_t* __restrict__ startbit, uint32_t t_begin, uint32_t t_end,
                                uint32_t k_eff, long long col_len, long long col_start, long long row_a,
                                long long total) {
@@ -628,7 +656,7 @@ __device__ void decode_generic(const Smem& sm, const mps_bucket_tensor& T, int m
         for (long long e = t; e < total; e += k_eff) {
             const long long rr = e / col_len, cc = e - rr * col_len;
             long long base;
-            if (rr < kRowCap && small) base = (sm.rowbase[rr] == 0xFFFFFFFFu) ? -1 : (long long)sm.rowbase[rr];
+            if (rr < kRowCap && small) base = (rowbase[rr] == 0xFFFFFFFFu) ? -1 : (long long)rowbase[rr];
             else {
                 const long long row = T.row_indices[row_a + rr];
                 const long long c0 = (mode == 2) ? (long long)T.group_col_start[row_a + rr] : col_start;
@@ -659,7 +687,7 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
     const bool aligned = ((reinterpret_cast<uintptr_t>(T.decode_syms) & 15u) == 0) &&
                          ((reinterpret_cast<uintptr_t>(T.decode_lens) & 3u) == 0);
     bool esc = false;
-    for (int it0 = 0; it0 < ITERS && tid < THREADS; it0 += BATCH) {
+    for (int it0 = 0; it0 < ITERS; it0 += BATCH) {
         uint4 sv[BATCH];
         uint32_t lv[BATCH];
         int32_t gv[BATCH];
@@ -718,20 +746,111 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
             dst[1] = make_uint4(ent[4], ent[5], ent[6], ent[7]);
         }
     }
-    return __syncthreads_or(esc ? 1 : 0) != 0;
+    return group_or(esc ? 1 : 0, THREADS) != 0;
 }
 
 template <int L, int THREADS, int CH>
-__global__ void __launch_bounds__(THREADS + 32, 1)
+__device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws, int slot, bool prefix_cached) {
+    constexpr int NCTX = (L == 7) ? 256 : 16;
+    constexpr int TS = 1 << L;
+    constexpr uint32_t SPAN = THREADS * CH;
+    const int lane = threadIdx.x & 31;
+    Prepared& P = sm.prep[slot];
+    int item = 0;
+    if (lane == 0) item = (int)atomicAdd(&ws[0], 1u);
+    item = __shfl_sync(0xFFFFFFFFu, item, 0);
+    if (item >= args.total_items) {
+        if (lane == 0) P.valid = 0;
+        __syncwarp();
+        return;
+    }
+    int ti = 0;
+    long long local = item;
+    if (args.tensors != nullptr) {
+        int lo = 0, hi = args.count;  // largest ti with prefix[ti] <= item
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            const long long p = prefix_cached ? sm.prefix[mid] : args.item_prefix[mid];
+            if (p <= item) lo = mid; else hi = mid;
+        }
+        ti = lo;
+        local = item - (prefix_cached ? sm.prefix[ti] : args.item_prefix[ti]);
+    }
+    const mps_bucket_tensor& T = (args.tensors != nullptr) ? args.tensors[ti] : args.single;
+    const int mode = T.mode;
+    const uint32_t k = (uint32_t)T.k;
+    const uint32_t chunks = (k + SPAN - 1) / SPAN;
+    const long long b = local / chunks;
+    const uint32_t chunk = (uint32_t)(local - b * chunks);
+    const long long row_a = T.bucket_row_offsets[b];
+    const long long nrows = (long long)T.bucket_row_offsets[b + 1] - row_a;
+    long long col_start = 0, col_len = T.group_size;
+    if (mode != 2) { col_start = T.bucket_col_start[b]; col_len = T.bucket_col_len[b]; }
+    const long long total = nrows * col_len;
+    bool ok = nrows > 0 && col_len > 0 && row_a >= 0 && row_a + nrows <= T.num_rows &&
+              (mode == 2 || (col_start >= 0 && col_start + col_len <= T.m));
+    const long long bit_base = T.bucket_bit_base[b];
+    const long long wb = bit_base >> 6;
+    ok = ok && bit_base >= 0 && wb < T.bitstream_words;
+    uint32_t k_eff = k;
+    if (total < (long long)k_eff) k_eff = (uint32_t)(total > 0 ? total : 1);
+    const uint32_t t_begin = chunk * SPAN;
+    ok = ok && t_begin < k_eff;
+
+    int rows_ok = 1, rows_vec = 1, rows_al16 = 1;
+    uint32_t ebits = 0;
+    if (ok) {
+        const uint32_t* startbit = T.thread_startbit + b * ((long long)k + 1);
+        ebits = startbit[k_eff];
+        // row bases of the bucket (element offset of each row / group start)
+        const long long ncache = nrows < kRowCap ? nrows : kRowCap;
+        for (long long i = lane; i < ncache; i += 32) {
+            const long long row = T.row_indices[row_a + i];
+            const long long c0 = (mode == 2) ? (long long)T.group_col_start[row_a + i] : col_start;
+            const bool good = row >= 0 && row < T.n && c0 >= 0 && c0 + col_len <= T.m;
+            const long long base = row * T.m + c0;
+            sm.rowbase[slot][i] = (good && base < 0xFFFFFFFFLL) ? (uint32_t)base : 0xFFFFFFFFu;
+            rows_ok &= good;
+            rows_vec &= ((base & (CH - 1)) == 0);
+            rows_al16 &= ((base & 15) == 0);
+        }
+        rows_ok = __all_sync(0xFFFFFFFFu, rows_ok);
+        rows_vec = __all_sync(0xFFFFFFFFu, rows_vec);
+        rows_al16 = __all_sync(0xFFFFFFFFu, rows_al16);
+        // pull what the item will read first into L2: its tables, its sub-stream offsets
+        for (int c = lane; c < NCTX; c += 32) {
+            const int32_t gid = T.bucket_table[b * NCTX + c];
+            if (gid >= 0 && gid < T.num_tables) {
+                const uint8_t* sp = reinterpret_cast<const uint8_t*>(T.decode_syms + (long long)gid * TS);
+                const uint8_t* lp = T.decode_lens + (long long)gid * (TS / 2);
+                for (int o = 0; o < TS * 2; o += 128) prefetch_l2(sp + o);
+                for (int o = 0; o < TS / 2; o += 128) prefetch_l2(lp + o);
+            }
+        }
+        const uint8_t* sb = reinterpret_cast<const uint8_t*>(startbit + t_begin);
+        for (uint32_t o = lane * 128u; o < SPAN * 4u; o += 32u * 128u) prefetch_l2(sb + o);
+    }
+    if (lane == 0) {
+        P.valid = 1; P.ok = ok ? 1 : 0; P.ti = ti; P.mode = mode;
+        P.k = k; P.k_eff = k_eff; P.t_begin = t_begin; P.ebits = ebits;
+        P.b = b; P.row_a = row_a; P.nrows = nrows; P.col_start = col_start; P.col_len = col_len; P.total = total; P.wb = wb;
+        P.rows_ok = rows_ok; P.rows_vec = rows_vec; P.rows_al16 = rows_al16;
+    }
+    __syncwarp();
+}
+
+template <int L, int THREADS, int CH>
+__global__ void __launch_bounds__(THREADS + 64, 1)
 bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __restrict__ ws) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
     constexpr int NCTX = (L == 7) ? 256 : 16;
     constexpr uint32_t SPAN = THREADS * CH;  // sub-streams per work item
-    constexpr int NT = THREADS + 32;         // THREADS decoding threads + one producer warp
+    constexpr int NT = THREADS + 64;         // decoding threads + producer warp + scout warp
     const int tid = threadIdx.x;
     const bool is_consumer = tid < THREADS;
-    const bool is_producer = tid == THREADS;  // first lane of the extra warp
+    const bool is_producer = tid == THREADS;        // first lane of the producer warp
+    const bool is_scout = tid >= THREADS + 32;       // the whole scout warp
 
     const bool prefix_cached = args.tensors != nullptr && args.count <= kPrefixCap;
     if (prefix_cached)
@@ -747,166 +866,119 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    if (is_scout) scout_prepare<L, THREADS, CH>(args, sm, ws, 0, prefix_cached);
+    __syncthreads();
 
     bool staged_esc = false;
     uint32_t blk = 0;  // blocks of steps streamed so far by this CTA (same value in every thread)
-    for (;;) {
+    for (int iter = 0;; ++iter) {
         MPS_T0();
-        if (tid == 0) sm.item = (int)atomicAdd(&ws[0], 1u);
-        __syncthreads();
-        const int item = sm.item;
-        if (item >= args.total_items) break;
+        const int slot = iter & 1;
+        const Prepared& P = sm.prep[slot];
+        if (!P.valid) break;
+        if (is_scout) {
+            // next item's geometry, row bases and L2 prefetches, while the others decode this one
+            scout_prepare<L, THREADS, CH>(args, sm, ws, slot ^ 1, prefix_cached);
+        } else if (P.ok) {
+            const int ti = P.ti, mode = P.mode;
+            const mps_bucket_tensor& T = (args.tensors != nullptr) ? args.tensors[ti] : args.single;
+            const uint32_t k = P.k, k_eff = P.k_eff, t_begin = P.t_begin;
+            const long long b = P.b, row_a = P.row_a, nrows = P.nrows, col_start = P.col_start, col_len = P.col_len;
+            const long long total = P.total, wb = P.wb;
+            const uint32_t* rowbase = sm.rowbase[slot];
+            const uint32_t* bs32 = reinterpret_cast<const uint32_t*>(T.bitstream) + 2 * wb;
+            const long long units = 2 * (T.bitstream_words - wb);
+            const uint32_t lim = (uint32_t)((units > 0x7FFFFFFELL ? 0x7FFFFFFELL : units) - 1);  // odd: r <= lim <=> r^1 <= lim
+            const uint32_t* startbit = T.thread_startbit + b * ((long long)k + 1);
+            const bool vec = P.rows_ok && P.rows_vec && nrows <= kRowCap && (k_eff % CH) == 0 && (col_len % CH) == 0 &&
+                             T.n * T.m < 0xFFFFFFFFLL && ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & (CH - 1)) == 0) &&
+                             ((reinterpret_cast<uintptr_t>(T.out) & (2 * CH - 1)) == 0);
 
-        // ---- item -> (tensor, bucket, chunk) --------------------------------------------------
-        int ti = 0;
-        long long local = item;
-        if (args.tensors != nullptr) {
-            int lo = 0, hi = args.count;  // largest ti with prefix[ti] <= item
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                const long long p = prefix_cached ? sm.prefix[mid] : args.item_prefix[mid];
-                if (p <= item) lo = mid; else hi = mid;
+            // ---- streaming path: start the asynchronous copies before the tables are staged ------------
+            StreamItem it;
+            StreamThread<L, THREADS, CH> st;
+            bool stream = false;
+            if (vec && P.rows_al16 && t_begin + SPAN <= k_eff && (col_len % k_eff) == 0 && (k_eff % 16u) == 0 &&
+                ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & 15u) == 0) && !MPS_NO_STREAM) {
+                const uint8_t* bucket_bytes = reinterpret_cast<const uint8_t*>(T.bitstream) + 8 * wb;
+                const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(bucket_bytes) & 15u);  // 0 or 8
+                const long long valid = 8 * (T.bitstream_words - wb) + mis;
+                const long long bits = (long long)P.ebits + 8 * mis;  // end of the bucket's bits from the origin
+                // every chunk a valid sub-stream can ask for (kRingChunks ahead of its last unit) must exist
+                if ((mis == 0u || wb > 0) && valid <= 0x7FFFFFF0LL && (bits >> 3) + 16 * (kRingChunks + 2) <= valid) {
+                    stream = true;
+                    it.ctx_bytes = T.ctx_bytes; it.out = T.out; it.startbit = startbit; it.rowbase = rowbase;
+                    it.bo.base = bucket_bytes - mis; it.bo.last_ofs = (uint32_t)((valid - 16) & ~15LL); it.bo.bit_delta = 8 * mis;
+                    it.t_begin = t_begin; it.k_eff = k_eff; it.col_len = (uint32_t)col_len;
+                    it.nsteps = (uint32_t)(total / k_eff);
+                }
             }
-            ti = lo;
-            local = item - (prefix_cached ? sm.prefix[ti] : args.item_prefix[ti]);
-        }
-        const mps_bucket_tensor& T = (args.tensors != nullptr) ? args.tensors[ti] : args.single;
-        const int mode = T.mode;
-        const uint32_t k = (uint32_t)T.k;
-        const uint32_t chunks = (k + SPAN - 1) / SPAN;
-        const long long b = local / chunks;
-        const uint32_t chunk = (uint32_t)(local - b * chunks);
+            MPS_TICK(0);  // geometry
+            bool run_ok = true;
+            uint32_t nblocks = 0;
+            if (stream) nblocks = (it.nsteps + kSS - 1) / kSS;
+            if (is_producer) {
+                if (stream) {
+                    uint32_t p_next = 0, p_rr = 0, p_cc = 0;
+                    run_ok = producer_run<SPAN>(sm, it, blk, p_next, p_rr, p_cc, nblocks);
+                }
+            } else if (is_consumer) {
+                if (stream) stream_begin<L, THREADS, CH>(sm, it, st);
+                MPS_TICK(2);  // async copies started
 
-        // ---- bucket geometry ------------------------------------------------------------------
-        const long long row_a = T.bucket_row_offsets[b];
-        const long long nrows = (long long)T.bucket_row_offsets[b + 1] - row_a;
-        long long col_start = 0, col_len = T.group_size;
-        if (mode != 2) { col_start = T.bucket_col_start[b]; col_len = T.bucket_col_len[b]; }
-        const long long total = nrows * col_len;
-        bool ok = nrows > 0 && col_len > 0 && row_a >= 0 && row_a + nrows <= T.num_rows &&
-                  (mode == 2 || (col_start >= 0 && col_start + col_len <= T.m));
-        const long long bit_base = T.bucket_bit_base[b];
-        const long long wb = bit_base >> 6;
-        ok = ok && bit_base >= 0 && wb < T.bitstream_words;
-        uint32_t k_eff = k;
-        if (total < (long long)k_eff) k_eff = (uint32_t)(total > 0 ? total : 1);
-        const uint32_t t_begin = chunk * SPAN;
-        if (!ok || t_begin >= k_eff) { __syncthreads(); continue; }  // uniform across the CTA
-
-        MPS_TICK(0);  // item fetch + geometry
-        // ---- row bases (element offset of each row / group start) ----------------------------------
-        int rows_ok = 1, rows_vec = 1, rows_al16 = 1;
-        const long long ncache = nrows < kRowCap ? nrows : kRowCap;
-        for (long long i = tid; i < ncache; i += NT) {
-            const long long row = T.row_indices[row_a + i];
-            const long long c0 = (mode == 2) ? (long long)T.group_col_start[row_a + i] : col_start;
-            const bool good = row >= 0 && row < T.n && c0 >= 0 && c0 + col_len <= T.m;
-            const long long base = row * T.m + c0;
-            sm.rowbase[i] = (good && base < 0xFFFFFFFFLL) ? (uint32_t)base : 0xFFFFFFFFu;
-            rows_ok &= good;
-            rows_vec &= ((base & (CH - 1)) == 0);
-            rows_al16 &= ((base & 15) == 0);
-        }
-        rows_ok = __syncthreads_and(rows_ok);
-        rows_vec = __syncthreads_and(rows_vec);
-        rows_al16 = __syncthreads_and(rows_al16);
-
-        const uint32_t* bs32 = reinterpret_cast<const uint32_t*>(T.bitstream) + 2 * wb;
-        const long long units = 2 * (T.bitstream_words - wb);
-        const uint32_t lim = (uint32_t)((units > 0x7FFFFFFELL ? 0x7FFFFFFELL : units) - 1);  // odd: r <= lim <=> r^1 <= lim
-        const uint32_t* startbit = T.thread_startbit + b * ((long long)k + 1);
-
-        const bool vec = rows_ok && rows_vec && nrows <= kRowCap && (k_eff % CH) == 0 &&
-                         (col_len % CH) == 0 && T.n * T.m < 0xFFFFFFFFLL &&
-                         ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & (CH - 1)) == 0) &&
-                         ((reinterpret_cast<uintptr_t>(T.out) & (2 * CH - 1)) == 0);
-
-        // ---- streaming path: start the asynchronous copies before the tables are staged ----------------
-        StreamItem it;
-        StreamThread<L, THREADS, CH> st;
-        bool stream = false;
-        if (vec && rows_al16 && t_begin + SPAN <= k_eff && (col_len % k_eff) == 0 && (k_eff % 16u) == 0 &&
-            ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & 15u) == 0) && !MPS_NO_STREAM) {
-            const uint8_t* bucket_bytes = reinterpret_cast<const uint8_t*>(T.bitstream) + 8 * wb;
-            const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(bucket_bytes) & 15u);  // 0 or 8
-            const long long valid = 8 * (T.bitstream_words - wb) + mis;
-            const long long bits = (long long)startbit[k_eff] + 8 * mis;  // end of the bucket's bits from the origin
-            // every chunk a valid sub-stream can ask for (kRingChunks ahead of its last unit) must exist
-            if ((mis == 0u || wb > 0) && valid <= 0x7FFFFFF0LL && (bits >> 3) + 16 * (kRingChunks + 2) <= valid) {
-                stream = true;
-                it.ctx_bytes = T.ctx_bytes; it.out = T.out; it.startbit = startbit;
-                it.bo.base = bucket_bytes - mis; it.bo.last_ofs = (uint32_t)((valid - 16) & ~15LL); it.bo.bit_delta = 8 * mis;
-                it.t_begin = t_begin; it.k_eff = k_eff; it.col_len = (uint32_t)col_len;
-                it.nsteps = (uint32_t)(total / k_eff);
-            }
-        }
-        MPS_TICK(1);  // row bases
-        bool run_ok = true;
-        uint32_t p_next = 0, p_rr = 0, p_cc = 0, nblocks = 0;
-        if (stream) {
-            nblocks = (it.nsteps + kSS - 1) / kSS;
-            if (is_consumer) stream_begin<L, THREADS, CH>(sm, it, st);
-            else if (is_producer)  // every stage is free at the start of an item: no waiting here
-                run_ok = producer_run<SPAN>(sm, it, blk, p_next, p_rr, p_cc, nblocks < (uint32_t)kStages ? nblocks : kStages);
-        }
-        MPS_TICK(2);  // async copies started
-
-        // ---- tables: restage only when the context->table map changed ----------------------------
-        constexpr int CPT = (NCTX + THREADS - 1) / THREADS;  // contexts per thread
-        int differs = (sm.staged_tensor != ti);
-        int32_t my_gid[CPT];
+                // ---- tables: restage only when the context->table map changed ------------------------
+                constexpr int CPT = (NCTX + THREADS - 1) / THREADS;  // contexts per thread
+                int differs = (sm.staged_tensor != ti);
+                int32_t my_gid[CPT];
 #pragma unroll
-        for (int i = 0; i < CPT; ++i) {
-            const int c = tid + i * THREADS;
-            my_gid[i] = -1;
-            if (is_consumer && c < NCTX) {
-                my_gid[i] = T.bucket_table[b * NCTX + c];
-                if (my_gid[i] >= T.num_tables) my_gid[i] = -1;
-                differs |= (my_gid[i] != sm.gid[c]);
-            }
-        }
-        differs = __syncthreads_or(differs);
-        if (differs) {
+                for (int i = 0; i < CPT; ++i) {
+                    const int c = tid + i * THREADS;
+                    my_gid[i] = -1;
+                    if (c < NCTX) {
+                        my_gid[i] = T.bucket_table[b * NCTX + c];
+                        if (my_gid[i] >= T.num_tables) my_gid[i] = -1;
+                        differs |= (my_gid[i] != sm.gid[c]);
+                    }
+                }
+                differs = group_or(differs, THREADS);
+                if (differs) {
 #pragma unroll
-            for (int i = 0; i < CPT; ++i) {
-                const int c = tid + i * THREADS;
-                if (is_consumer && c < NCTX) sm.gid[c] = my_gid[i];
-            }
-            if (tid == 0) sm.staged_tensor = ti;
-            __syncthreads();
-            staged_esc = stage_tables<L, THREADS>(sm, T, tid);
-        }
+                    for (int i = 0; i < CPT; ++i) {
+                        const int c = tid + i * THREADS;
+                        if (c < NCTX) sm.gid[c] = my_gid[i];
+                    }
+                    if (tid == 0) sm.staged_tensor = ti;
+                    group_sync(THREADS);
+                    staged_esc = stage_tables<L, THREADS>(sm, T, tid);
+                }
+                MPS_TICK(3);  // tables
 
-        MPS_TICK(3);  // tables
-        // ---- decode ------------------------------------------------------------------------------
-        const uint32_t t0 = t_begin + (uint32_t)tid * CH;
-        if (stream) {
-            if (is_consumer) {
-                run_ok = staged_esc ? stream_run<L, THREADS, CH, true>(sm, it, st, blk)
-                                    : stream_run<L, THREADS, CH, false>(sm, it, st, blk);
-            } else if (is_producer && run_ok) {
-                run_ok = producer_run<SPAN>(sm, it, blk, p_next, p_rr, p_cc, nblocks);
+                // ---- decode --------------------------------------------------------------------------
+                const uint32_t t0 = t_begin + (uint32_t)tid * CH;
+                if (stream) {
+                    run_ok = staged_esc ? stream_run<L, THREADS, CH, true>(sm, it, st, blk)
+                                        : stream_run<L, THREADS, CH, false>(sm, it, st, blk);
+                } else if (vec) {
+                    if (t0 < k_eff) {
+                        if (staged_esc)
+                            decode_vec<L, CH, true>(sm, rowbase, T.ctx_bytes, T.out, bs32, lim, startbit, t0, k_eff,
+                                                    (uint32_t)col_len, (uint32_t)nrows, (uint32_t)total);
+                        else
+                            decode_vec<L, CH, false>(sm, rowbase, T.ctx_bytes, T.out, bs32, lim, startbit, t0, k_eff,
+                                                     (uint32_t)col_len, (uint32_t)nrows, (uint32_t)total);
+                    }
+                } else if (t0 < k_eff) {
+                    const uint32_t t1 = (t0 + CH < k_eff) ? t0 + CH : k_eff;
+                    decode_generic<L>(sm, rowbase, T, mode, bs32, lim, startbit, t0, t1, k_eff, col_len, col_start, row_a,
+                                      total);
+                }
+                MPS_TICK(stream ? 4 : 5);  // decode (streaming / other paths), thread 0's own share
             }
             if (!run_ok) sm.abort = 1;
             blk += nblocks;
-        } else if (!is_consumer) {
-            // the producer warp has nothing to do on the non-streaming paths
-        } else if (vec) {
-            if (t0 < k_eff) {
-                if (staged_esc)
-                    decode_vec<L, CH, true>(sm, T.ctx_bytes, T.out, bs32, lim, startbit, t0, k_eff, (uint32_t)col_len,
-                                            (uint32_t)nrows, (uint32_t)total);
-                else
-                    decode_vec<L, CH, false>(sm, T.ctx_bytes, T.out, bs32, lim, startbit, t0, k_eff, (uint32_t)col_len,
-                                             (uint32_t)nrows, (uint32_t)total);
-            }
-        } else if (t0 < k_eff) {
-            const uint32_t t1 = (t0 + CH < k_eff) ? t0 + CH : k_eff;
-            decode_generic<L>(sm, T, mode, bs32, lim, startbit, t0, t1, k_eff, col_len, col_start, row_a, total);
         }
-        MPS_TICK(stream ? 4 : 5);  // decode (streaming / other paths), thread 0's own share
-        __syncthreads();  // everyone is done with tbl / rowbase / item before they are overwritten
-        MPS_TICK(6);  // waiting for the slowest warp
+        __syncthreads();  // item done: tables, rings and the other prepared slot may now be overwritten
+        MPS_TICK(6);      // waiting for the slowest warp
         if (sm.abort) {   // a bounded wait ran out: report and stop taking work (uniform: read after the barrier)
             if (tid == 0) atomicOr(&ws[2], 1u);
             break;
@@ -954,7 +1026,7 @@ static int launch_cfg(const BatchArgs& a, unsigned int* ws, cudaStream_t st) {
     int grid = sm_count();
     if (a.total_items < grid) grid = a.total_items;
     if (grid <= 0) return MPS_OK;
-    bucket_decode_kernel<L, THREADS, CH><<<grid, THREADS + 32, smem, st>>>(a, ws);
+    bucket_decode_kernel<L, THREADS, CH><<<grid, THREADS + 64, smem, st>>>(a, ws);
     MPS_CUDA_TRY(cudaGetLastError());
     return MPS_OK;
 }
