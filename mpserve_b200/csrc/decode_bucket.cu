@@ -52,7 +52,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 // ------------------------------------------------------------------------------------------------
 constexpr int kTableEntries = 32768;  // 256 ctx x 2^7 == 16 ctx x 2^11
 constexpr int kRowCap = 1024;         // rows / groups of a bucket cached in shared memory
-constexpr int kPrefixCap = 128;       // tensors of a batch whose item prefix is cached in shared memory
+constexpr int kPrefixCap = 64;        // tensors of a batch whose item prefix is cached in shared memory
 constexpr int kSteps = 4;             // steps per software-pipeline block (register-prefetch path)
 constexpr int kSS = 8;                // steps per stage of the streaming path's context ring
 #ifndef MPS_LOOK
@@ -91,7 +91,7 @@ struct Prepared {
     int rows_ok, rows_vec, rows_al16;
 };
 
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(p)); }
 
 // consumer-only barrier (id 1) with an OR reduction
 __device__ __forceinline__ int group_or(int pred, int nthreads) {
@@ -113,12 +113,21 @@ struct Smem {
     long long prefix[kPrefixCap + 1];
     unsigned long long full_bar[kStages];        // bulk copies of a stage have landed
     unsigned long long empty_bar[kStages];       // every warp is done reading a stage
-    int32_t gid[256];
+    int32_t gid[256];                            // context -> table id of the staged tables
+    int32_t gid_next[256];                       // same for the prepared item (written by the scout once the
+                                                 // decoding warps have taken the previous contents)
+    int gid_taken;                               // iteration whose gid_next has been consumed
     int staged_tensor;
     int abort;                                   // a bounded wait gave up
 };
 
-constexpr uint32_t kEscBit = 0x8000u;
+// Entry layout.  L=7 (FP8): sym << 16 | raw length nibble (bits 0-2 code length, bit 3 = ESC), which a
+// byte permute builds straight from the sidecar's packed arrays.  L=11 (AWQ): sym << 16 | esc << 15 |
+// code length (lengths there go up to 11, so the ESC flag cannot share the low nibble).
+template <int L> struct Entry {
+    static constexpr uint32_t kEsc = (L == 7) ? 0x8u : 0x8000u;
+    static constexpr uint32_t kLenMask = (L == 7) ? 0x7u : 0xFu;
+};
 
 // Optional per-phase cycle counters (tuning builds only: -DMPS_PHASE_TIMERS): thread 0 of every CTA
 // adds its clock deltas to ws[8 + 2*phase] (64-bit) so a host script can print the split.
@@ -145,17 +154,17 @@ template <> struct Ctx<1> {
 template <> struct Ctx<2> {
     using T = uint32_t;
     static __device__ __forceinline__ T ld(const uint8_t* p) { return ld_stream_u16(p); }
-    static __device__ __forceinline__ uint32_t byte(T v, int c) { return (v >> (8 * c)) & 0xFFu; }
+    static __device__ __forceinline__ uint32_t byte(T v, int c) { return __byte_perm(v, 0u, 0x4440u | (uint32_t)c); }
 };
 template <> struct Ctx<4> {
     using T = uint32_t;
     static __device__ __forceinline__ T ld(const uint8_t* p) { return ld_stream_u32(p); }
-    static __device__ __forceinline__ uint32_t byte(T v, int c) { return (v >> (8 * c)) & 0xFFu; }
+    static __device__ __forceinline__ uint32_t byte(T v, int c) { return __byte_perm(v, 0u, 0x4440u | (uint32_t)c); }
 };
 template <> struct Ctx<8> {
     using T = uint2;
     static __device__ __forceinline__ T ld(const uint8_t* p) { return ld_stream_u64(p); }
-    static __device__ __forceinline__ uint32_t byte(T v, int c) { return (((c < 4) ? v.x : v.y) >> (8 * (c & 3))) & 0xFFu; }
+    static __device__ __forceinline__ uint32_t byte(T v, int c) { return __byte_perm((c < 4) ? v.x : v.y, 0u, 0x4440u | (uint32_t)(c & 3)); }
 };
 
 // symbols sit in the HIGH half of an entry
@@ -301,8 +310,8 @@ __device__ __forceinline__ void decode_vec(const Smem& sm, const uint32_t* rowba
                         hi[c] = __funnelshift_l(0u, hi[c], e[c]);  // shift by the low 5 bits = code length
                         acc[c] += e[c];                            // low half accumulates the lengths
                     } else {
-                        uint32_t used = e[c] & 0xFu;
-                        if (e[c] & kEscBit) {                     // 16 raw bits follow the ESC code
+                        uint32_t used = e[c] & Entry<L>::kLenMask;
+                        if (e[c] & Entry<L>::kEsc) {                     // 16 raw bits follow the ESC code
                             e[c] = __funnelshift_l(0u, hi[c], used) & 0xFFFF0000u;
                             used += 16;
                         }
@@ -535,7 +544,7 @@ template <int L, int THREADS, int CH, bool ESC>
 __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st,
                                            uint32_t blk) {
     constexpr int RP = ESC ? 1 : ((32 - L) / L + 1);   // symbols per 32-bit window
-    constexpr int CHK = ESC ? 4 : kSS;                   // steps between bitstream requests
+    constexpr int CHK = ESC ? 4 : ((2 * kSS * L < 128) ? 2 * kSS : kSS);  // steps between bitstream requests
     constexpr int MAXBITS = ESC ? (L + 16) : L;          // most bits one step can consume
     static_assert(CHK * MAXBITS < 128, "at most one chunk boundary between two requests");
     // A chunk requested when w1 enters chunk k is first read when w1 enters chunk k + kRingChunks - 1,
@@ -544,7 +553,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
     constexpr int NEED = ((kRingChunks - 1) * 128 + MAXBITS - 1) / MAXBITS;
     constexpr int LAG = (NEED / CHK - 2) > 0 ? (NEED / CHK - 2) : 0;
     constexpr uint32_t SPAN = THREADS * CH;
-    static_assert(kSS % RP == 0 && kSS % CHK == 0, "a stage must hold whole windows and request periods");
+    static_assert(kSS % RP == 0 && (kSS % CHK == 0 || CHK == 2 * kSS), "a stage must hold whole windows and request periods");
     using CT = typename Ctx<CH>::T;
     const uint32_t tid = threadIdx.x;
     const uint32_t tbl = smem_u32(sm.tbl);
@@ -597,8 +606,8 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                         hi[c] = __funnelshift_l(0u, hi[c], e[c]);  // shift by the low 5 bits = code length
                         acc[c] += e[c];                            // low half accumulates the lengths
                     } else {
-                        uint32_t used = e[c] & 0xFu;
-                        if (e[c] & kEscBit) {                     // 16 raw bits follow the ESC code
+                        uint32_t used = e[c] & Entry<L>::kLenMask;
+                        if (e[c] & Entry<L>::kEsc) {                     // 16 raw bits follow the ESC code
                             e[c] = __funnelshift_l(0u, hi[c], used) & 0xFFFF0000u;
                             used += 16;
                         }
@@ -613,7 +622,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                     ++c_rr;
                     outp = it.out + (it.rowbase[c_rr < kRowCap ? c_rr : 0] + t0);
                 }
-                if ((u + 1) % CHK == 0) {
+                if ((CHK <= kSS) ? ((u + 1) % CHK == 0) : (u == kSS - 1 && (jb & 1u))) {
                     // the position used for the request is the one of the last window; the bits consumed
                     // since then (< 32) can only make the request one period late, which NEED allows for
 #pragma unroll
@@ -634,8 +643,8 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
 template <int L>
 __device__ __forceinline__ uint32_t decode_one_win(BitWin& w, const uint32_t* __restrict__ tbl, uint32_t ctx) {
     const uint32_t e = tbl[(ctx << L) + (w.hi >> (32 - L))];
-    win_consume(w, e & 0xFu);
-    if (e & kEscBit) {
+    win_consume(w, e & Entry<L>::kLenMask);
+    if (e & Entry<L>::kEsc) {
         const uint32_t raw = w.hi >> 16;
         win_consume(w, 16);
         return raw;
@@ -723,20 +732,34 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
             const uint32_t s[4] = {sv[q].x, sv[q].y, sv[q].z, sv[q].w};
             uint32_t ent[8];
             if (gv[q] >= 0) {
+                if constexpr (L == 7) {
+                    // nibbles i and i+4 of the eight, each alone in a 16-bit lane; one byte permute then
+                    // glues a symbol's two bytes above its nibble
+                    const uint32_t t = lv[q];
+                    esc |= (t & 0x88888888u) != 0u;
+                    const uint32_t z[4] = {t & 0x000F000Fu, (t >> 4) & 0x000F000Fu, (t >> 8) & 0x000F000Fu,
+                                           (t >> 12) & 0x000F000Fu};
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t sym = (s[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
-                    const uint32_t nib = (lv[q] >> (4 * i)) & 0xFu;
-                    uint32_t len, e;
-                    if constexpr (L == 7) { len = nib & 7u; e = nib >> 3; }   // bit 3 = ESC, low 3 bits = code length
-                    else { e = (nib == 15u); len = e ? (uint32_t)L : nib; }    // nibble 15 = ESC with an L-bit code
-                    esc |= (e != 0);
-                    ent[i] = (sym << 16) | (e << 15) | len;
+                    for (int i = 0; i < 8; ++i) {
+                        // bytes: [nibble, 0, sym.lo, sym.hi]; operand a = z (bytes 0-3), b = syms (bytes 4-7)
+                        const uint32_t sel = ((i & 1) ? 0x7600u : 0x5400u) | ((i & 4) ? 0x32u : 0x10u);
+                        ent[i] = __byte_perm(z[i & 3], s[i >> 1], sel);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t sym = (s[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+                        const uint32_t nib = (lv[q] >> (4 * i)) & 0xFu;
+                        const uint32_t e = (nib == 15u);            // nibble 15 = ESC with an L-bit code
+                        const uint32_t len = e ? (uint32_t)L : nib;
+                        esc |= (e != 0);
+                        ent[i] = (sym << 16) | (e << 15) | len;
+                    }
                 }
             } else {
                 // no table for this context: the FP8 decoder emits zeros and consumes nothing
                 // (decode_huffman.cu:252-264); the AWQ decoders treat it as an ESC (:476-485).
-                const uint32_t fill = (L == 7) ? 0u : ((uint32_t)L | kEscBit);
+                const uint32_t fill = (L == 7) ? 0u : ((uint32_t)L | Entry<L>::kEsc);
                 esc |= (L != 7);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) ent[i] = fill;
@@ -750,7 +773,8 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
 }
 
 template <int L, int THREADS, int CH>
-__device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws, int slot, bool prefix_cached) {
+__device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws, int slot, bool prefix_cached,
+                              int wait_iter) {
     constexpr int NCTX = (L == 7) ? 256 : 16;
     constexpr int TS = 1 << L;
     constexpr uint32_t SPAN = THREADS * CH;
@@ -818,9 +842,18 @@ __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws,
         rows_vec = __all_sync(0xFFFFFFFFu, rows_vec);
         rows_al16 = __all_sync(0xFFFFFFFFu, rows_al16);
         // pull what the item will read first into L2: its tables, its sub-stream offsets
-        for (int c = lane; c < NCTX; c += 32) {
-            const int32_t gid = T.bucket_table[b * NCTX + c];
-            if (gid >= 0 && gid < T.num_tables) {
+        int32_t gids[(NCTX + 31) / 32];
+#pragma unroll
+        for (int j = 0; j < (NCTX + 31) / 32; ++j) {
+            const int c = lane + 32 * j;
+            int32_t gid = (c < NCTX) ? T.bucket_table[b * NCTX + c] : -1;
+            if (gid >= T.num_tables) gid = -1;
+            gids[j] = gid;
+        }
+#pragma unroll
+        for (int j = 0; j < (NCTX + 31) / 32; ++j) {
+            const int32_t gid = gids[j];
+            if (gid >= 0) {
                 const uint8_t* sp = reinterpret_cast<const uint8_t*>(T.decode_syms + (long long)gid * TS);
                 const uint8_t* lp = T.decode_lens + (long long)gid * (TS / 2);
                 for (int o = 0; o < TS * 2; o += 128) prefetch_l2(sp + o);
@@ -829,6 +862,16 @@ __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws,
         }
         const uint8_t* sb = reinterpret_cast<const uint8_t*>(startbit + t_begin);
         for (uint32_t o = lane * 128u; o < SPAN * 4u; o += 32u * 128u) prefetch_l2(sb + o);
+        // hand the context -> table map over once the decoding warps have taken the previous one
+        if (wait_iter >= 0) {
+            volatile int* taken = &sm.gid_taken;
+            for (uint32_t spin = 0; spin < kSpinLimit && *taken != wait_iter; ++spin) {}
+        }
+#pragma unroll
+        for (int j = 0; j < (NCTX + 31) / 32; ++j) {
+            const int c = lane + 32 * j;
+            if (c < NCTX) sm.gid_next[c] = gids[j];
+        }
     }
     if (lane == 0) {
         P.valid = 1; P.ok = ok ? 1 : 0; P.ti = ti; P.mode = mode;
@@ -858,6 +901,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
     if (tid == 0) {
         sm.staged_tensor = -1;
         sm.abort = 0;
+        sm.gid_taken = 0;
         for (int i = 0; i < kStages; ++i) {
             mbar_init(smem_u32(&sm.full_bar[i]), 1u);
             mbar_init(smem_u32(&sm.empty_bar[i]), THREADS / 32);
@@ -866,7 +910,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-    if (is_scout) scout_prepare<L, THREADS, CH>(args, sm, ws, 0, prefix_cached);
+    if (is_scout) scout_prepare<L, THREADS, CH>(args, sm, ws, 0, prefix_cached, -1);
     __syncthreads();
 
     bool staged_esc = false;
@@ -878,7 +922,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         if (!P.valid) break;
         if (is_scout) {
             // next item's geometry, row bases and L2 prefetches, while the others decode this one
-            scout_prepare<L, THREADS, CH>(args, sm, ws, slot ^ 1, prefix_cached);
+            scout_prepare<L, THREADS, CH>(args, sm, ws, slot ^ 1, prefix_cached, iter + 1);
         } else if (P.ok) {
             const int ti = P.ti, mode = P.mode;
             const mps_bucket_tensor& T = (args.tensors != nullptr) ? args.tensors[ti] : args.single;
@@ -935,12 +979,12 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                     const int c = tid + i * THREADS;
                     my_gid[i] = -1;
                     if (c < NCTX) {
-                        my_gid[i] = T.bucket_table[b * NCTX + c];
-                        if (my_gid[i] >= T.num_tables) my_gid[i] = -1;
+                        my_gid[i] = sm.gid_next[c];
                         differs |= (my_gid[i] != sm.gid[c]);
                     }
                 }
                 differs = group_or(differs, THREADS);
+                if (tid == 0) *(volatile int*)&sm.gid_taken = iter + 1;  // the scout may now overwrite gid_next
                 if (differs) {
 #pragma unroll
                     for (int i = 0; i < CPT; ++i) {
@@ -977,6 +1021,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             if (!run_ok) sm.abort = 1;
             blk += nblocks;
         }
+        if (!P.ok && tid == 0) *(volatile int*)&sm.gid_taken = iter + 1;
         __syncthreads();  // item done: tables, rings and the other prepared slot may now be overwritten
         MPS_TICK(6);      // waiting for the slowest warp
         if (sm.abort) {   // a bounded wait ran out: report and stop taking work (uniform: read after the barrier)
