@@ -1,0 +1,92 @@
+"""Multi-rank host logic on CPU (gloo, world_size 2): the shard partition covers the model exactly
+once and the all-reduced checksum of per-rank decodes equals the single-process one."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from mpserve_b200 import shard
+from mpserve_b200 import workloads as wl
+from oracle import oracle as orc
+
+TINY = dict(layers=2, hidden=64, inter=128, q_heads=4, kv_heads=2, head_dim=16, vocab=100)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _full_weight(name, n, m, li):
+    return wl.random_weight(n, m, 7000 + 13 * li + sum(name.encode()) % 97, "normal")  # no str hash: it differs per process
+
+
+def _rank_checksum(cfg, tp, rank):
+    acc = (0, 0)
+    for li in range(cfg["layers"]):
+        for name, n, m in wl.layer_linears(cfg):
+            w = shard.shard_of(name, _full_weight(name, n, m, li), tp, rank)
+            c = wl.quantize_fp8(w, "channel")
+            bits = c.bf16.view(torch.uint16).numpy()
+            art = orc.build_fp8(bits, c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 64)
+            dec = orc.decode_fp8(c.fp8_u8.numpy(), art, *bits.shape)
+            assert np.array_equal(dec, bits)
+            acc = shard.combine(acc, shard.checksum_host(dec))
+    return acc
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        local = _rank_checksum(TINY, world, rank)
+        total = shard.all_reduce_checksum(local)
+        q.put((rank, local, total))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_shards_tile_each_weight():
+    for name, n, m in wl.layer_linears(TINY):
+        w = _full_weight(name, n, m, 0)
+        parts = [shard.shard_of(name, w, 2, r) for r in range(2)]
+        dim = 1 if name.endswith(("o_proj", "down_proj")) else 0
+        assert torch.equal(torch.cat(parts, dim=dim), w)
+        assert tuple(parts[0].shape) == wl.tp_shard_shape(name, n, m, 2)
+
+
+def test_layer_partition_is_exact():
+    for world in (1, 2, 3, 8):
+        seen = [li for r in range(world) for li in shard.layers_of_rank(32, world, r)]
+        assert seen == list(range(32))
+
+
+def test_checksum_all_reduce_two_ranks_gloo():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    locals_ = {r: loc for r, loc, _ in results}
+    want = shard.combine(locals_[0], locals_[1])
+    for _, _, total in results:
+        assert total == want
+    # the sum part is independent of how the weights were sharded: whole weights give the same sum
+    whole = (0, 0)
+    for li in range(TINY["layers"]):
+        for name, n, m in wl.layer_linears(TINY):
+            bits = _full_weight(name, n, m, li).view(torch.uint16).numpy()
+            whole = shard.combine(whole, shard.checksum_host(bits))
+    assert whole[0] == want[0]
