@@ -132,6 +132,27 @@ MPS_API int mps_decode_awq_shared_table(const uint64_t* bitstream_u64, int64_t b
                                 const int32_t* stream_chunk_ids_i32, int64_t out_len, int64_t max_len,
                                 int16_t* out_i16, void* stream);
 
+/* No counterpart in the reference.  Same decode as mps_decode_fp8 for callers that must not allocate
+ * device memory and therefore cannot supply a workspace: code running inside another framework's
+ * memory pool or under a fixed memory budget, a plugin loaded into a process that forbids cudaMalloc
+ * after start-up, a real-time loop.  The work-queue counters live in a 256-byte array that is part of
+ * this library's device image (every GPU that loads the library holds it until the process exits);
+ * the call itself allocates and frees nothing.
+ *  - Limit: at most MPS_NOALLOC_MAX_BUCKETS buckets per call; more is rejected with MPS_ERR_INVALID.
+ *  - The first call on a device looks the array's device address up (once per device); make that first
+ *    call outside any stream capture.
+ *  - All calls share the one array: calls whose kernels may overlap on the GPU (different streams,
+ *    no ordering between them) race on it.  Calls on one stream, or otherwise ordered, are fine. */
+#define MPS_NOALLOC_MAX_BUCKETS (1 << 20)
+MPS_API int mps_decode_fp8_noalloc(const uint8_t* fp8_u8, const uint64_t* bitstream_u64, int64_t bitstream_words,
+                                   const uint16_t* decode_syms_u16, const uint8_t* decode_lens_u8, int64_t num_tables,
+                                   const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                                   const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                                   const int32_t* row_indices_i32, int64_t num_row_indices,
+                                   const uint32_t* bucket_thread_startbit_u32, const int64_t* bucket_bit_base_i64,
+                                   int64_t num_buckets, int32_t k, int64_t n, int64_t m, int64_t max_len,
+                                   uint16_t* out_bf16, void* stream);
+
 /* Many tensors in one launch (whole-model decompression).  `tensors_dev` is a DEVICE array of
  * `count` descriptors; `item_prefix_dev` a DEVICE array of count+1 int64 work-item prefix sums as
  * returned by mps_bucket_batch_plan for the same descriptors.  No reference counterpart: the

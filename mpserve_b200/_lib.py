@@ -38,6 +38,8 @@ _PROTOS = {
     "mps_workspace_bytes": (C.c_size_t, []),
     "mps_decode_fp8": (C.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _i32, _i64, _i64,
                                  _i64, _p, _p, C.c_size_t, _p]),
+    "mps_decode_fp8_noalloc": (C.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _i32, _i64, _i64,
+                                         _i64, _p, _p]),
     "mps_decode_awq_int4_bucket": (C.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _p, _p, _p, _i64, _p, _p, _i64, _i32,
                                              _i64, _i64, _i64, _p, _p, C.c_size_t, _p]),
     "mps_decode_awq_int4_bucket_by_scale": (C.c_int, [_p, _p, _i64, _p, _p, _i64, _p, _p, _p, _p, _i64, _p, _p, _i64,

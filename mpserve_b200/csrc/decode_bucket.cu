@@ -1172,6 +1172,30 @@ __global__ void checksum_u16_kernel(const uint16_t* __restrict__ d, long long co
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Scratch for callers that cannot allocate: the work-queue counters of ONE decode launch at a time,
+// resident in every GPU that loads this library until the process exits.
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 256;
+static __device__ __align__(256) unsigned int g_static_scratch[kStaticScratchBytes / sizeof(unsigned int)];
+
+// Device address of g_static_scratch on the current device.  In host code the array's name is only a
+// handle for the runtime, never a pointer a kernel may be given; the address is asked for once per
+// device (with that device current) and remembered.
+static int static_scratch(unsigned int** out) {
+    static unsigned int* cached[64] = {nullptr};
+    int dev = 0;
+    MPS_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) { set_error("device ordinal %d out of range for the static scratch", dev); return MPS_ERR_UNSUPPORTED; }
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        MPS_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        cached[dev] = static_cast<unsigned int*>(p);
+    }
+    *out = cached[dev];
+    return MPS_OK;
+}
+
 }  // namespace mps
 
 // ------------------------------------------------------------------------------------------------
@@ -1260,6 +1284,30 @@ int mps_decode_awq_int4_bucket_by_scale(const uint8_t* int4_values_u8, const uin
     T.num_buckets = num_buckets; T.k = k; T.group_size = (int32_t)group_size; T.mode = 2; T.n = n; T.m = m;
     T.out = out_bf16;
     return decode_single(T, 11, workspace, workspace_bytes, stream);
+}
+
+int mps_decode_fp8_noalloc(const uint8_t* fp8_u8, const uint64_t* bitstream_u64, int64_t bitstream_words,
+                           const uint16_t* decode_syms_u16, const uint8_t* decode_lens_u8, int64_t num_tables,
+                           const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                           const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                           const int32_t* row_indices_i32, int64_t num_row_indices,
+                           const uint32_t* bucket_thread_startbit_u32, const int64_t* bucket_bit_base_i64,
+                           int64_t num_buckets, int32_t k, int64_t n, int64_t m, int64_t max_len,
+                           uint16_t* out_bf16, void* stream) {
+    if (num_buckets > MPS_NOALLOC_MAX_BUCKETS) {
+        set_error("mps_decode_fp8_noalloc: %lld buckets exceed the supported maximum of %d", (long long)num_buckets,
+                  MPS_NOALLOC_MAX_BUCKETS);
+        return MPS_ERR_INVALID;
+    }
+    unsigned int* scratch = nullptr;
+    int rc = static_scratch(&scratch);
+    if (rc) return rc;
+    // every call shares the array and finds what the last one left: start from zeroed counters
+    MPS_CUDA_TRY(cudaMemsetAsync(scratch, 0, kStaticScratchBytes, static_cast<cudaStream_t>(stream)));
+    return mps_decode_fp8(fp8_u8, bitstream_u64, bitstream_words, decode_syms_u16, decode_lens_u8, num_tables,
+                          bucket_table_i32, bucket_col_start_i32, bucket_col_len_i32, bucket_row_offsets_i32,
+                          row_indices_i32, num_row_indices, bucket_thread_startbit_u32, bucket_bit_base_i64, num_buckets, k,
+                          n, m, max_len, out_bf16, scratch, kStaticScratchBytes, stream);
 }
 
 int mps_bucket_batch_plan(const mps_bucket_tensor* tensors_host, int count, int64_t* item_prefix_host,
