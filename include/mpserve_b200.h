@@ -163,6 +163,48 @@ MPS_API int mps_decode_bucket_batch(const mps_bucket_tensor* tensors_dev, const 
                             int64_t total_items, int32_t threads, int32_t chains, int32_t mode,
                             void* workspace, size_t workspace_bytes, void* stream);
 
+/* Sidecar builder -------------------------------------------------------------------------------
+ * Together these replace huffman_cpp::huffman_build_fp8_decode_tables_entry
+ * (kernel/build_huffman.cu:292-969; Python name huffman_build_fp8_decode_tables,
+ * kernel/wrapper.cpp:419-454) and huffman_build_awq_int4_bucket_decode_tables_entry
+ * (kernel/build_huffman.cu:1582-2126; wrapper.cpp:258-288).  All tensors are DEVICE pointers; the
+ * produced artifacts are byte-identical to the reference's.  The caller allocates outputs between
+ * the steps, whose sizes each step returns:
+ *   analyze      -> number of tables G          then allocate decode_syms [G,2^L], decode_lens [G,2^(L-1)]
+ *   codebooks    fills the tables and table_scale / table_ctx [G]
+ *   bucket_table fills bucket_table [B, 256|16] from the buckets' scales (bucket lists are built by
+ *                the caller from the scale tensor: build_huffman.cu:611-696)
+ *   rect_layout  fills bucket_thread_startbit [B,k+1] and bucket_bit_base [B+1], returns total bits
+ *   rect_emit    fills bitstream_u64 [(total_bits+63)/64]
+ * variant: 0 FP8 (context = fp8 byte), 1 AWQ-INT4 rectangular buckets (context = int4 code).
+ * scale_mode: 0 scalar, 1 per row [n], 2 two-dimensional blocks [n/sb0, nb1] of sb0 x sb1 elements. */
+typedef struct mps_build_state { unsigned char opaque[256]; } mps_build_state;
+
+MPS_API size_t mps_build_workspace_bytes(int64_t numel, int64_t substreams);
+MPS_API int mps_build_analyze(mps_build_state* state, const uint16_t* bf16_bits, const uint8_t* ctx_bytes,
+                              const uint16_t* scales_u16, int32_t scale_mode, int64_t nb1, int64_t sb0, int64_t sb1,
+                              int64_t n, int64_t m, int32_t variant, int64_t max_len, void* workspace,
+                              size_t workspace_bytes, void* stream, int64_t* num_tables_out, int64_t* num_items_out);
+MPS_API int mps_build_codebooks(mps_build_state* state, uint16_t* decode_syms_u16, uint8_t* decode_lens_u8,
+                                uint16_t* table_scale_u16, uint16_t* table_ctx_u16, void* stream);
+MPS_API int mps_build_bucket_table(mps_build_state* state, const uint16_t* bucket_scale_u16, int64_t num_buckets,
+                                   int32_t* bucket_table_i32, void* stream);
+/* bucket_U / bucket_unique_gid / bucket_fp8_uidx of the FP8 builder (build_huffman.cu:748-783) */
+MPS_API int mps_build_bucket_unique(const int32_t* bucket_table_i32, int64_t num_buckets, int32_t* bucket_U_i32,
+                                    int32_t* bucket_unique_gid_i32, int16_t* bucket_fp8_uidx_i16, void* stream);
+MPS_API int mps_build_rect_layout(mps_build_state* state, const uint16_t* bf16_bits, const uint8_t* ctx_bytes,
+                                  const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                                  const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                                  const int32_t* row_indices_i32, int64_t num_buckets, int32_t k,
+                                  uint32_t* bucket_thread_startbit_u32, int64_t* bucket_bit_base_i64, void* stream,
+                                  int64_t* total_bits_out);
+MPS_API int mps_build_rect_emit(mps_build_state* state, const uint16_t* bf16_bits, const uint8_t* ctx_bytes,
+                                const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                                const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                                const int32_t* row_indices_i32, int64_t num_buckets, int32_t k,
+                                const uint32_t* bucket_thread_startbit_u32, const int64_t* bucket_bit_base_i64,
+                                uint64_t* bitstream_u64, int64_t bitstream_words, void* stream);
+
 /* Checksum of a decoded tensor: sum of the 16-bit patterns (mod 2^64) and an XOR fold of
  * (pattern * (index+1)) -- what ranks all-reduce after a sharded decode.  result_dev: device
  * uint64[2], accumulated into (zero it first). */

@@ -13,7 +13,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "libmpserve_b200.so"
-SOURCES = ["decode_bucket.cu", "decode_shared.cu"]
+SOURCES = ["decode_bucket.cu", "decode_shared.cu", "encode.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

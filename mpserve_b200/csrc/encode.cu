@@ -1,0 +1,762 @@
+// GPU builder of the Huffman sidecar: replaces the single-threaded CPU encoder of the reference
+// (kernel/build_huffman.cu) with device passes that produce byte-identical artifacts.
+//
+//   analyze    composite keys (scale, context, symbol) -> radix sort -> run lengths: the histogram
+//              of every context (build_huffman.cu:392-412), contexts in ascending key order
+//   codebooks  per context: order by (count, symbol), ESC reduction when there are more symbols than
+//              table slots (:479-535), length-limited code lengths (package-merge, :46-118), canonical
+//              codes in item order (:171-203), lookup-table fill and 4-bit length packing (:205-239)
+//   layout     bits of every sub-stream (one thread per sub-stream, elements t, t+k_eff, ...), prefix
+//              sums per bucket, 64-bit aligned bucket bases (:811-879)
+//   emit       the same walk again, writing codes MSB-first with one 64-bit atomic OR per word (:881-911)
+//
+// The global sorts and scans use CUB (device-wide radix sort / run-length encode / scan from the
+// CUDA toolkit); everything codec-specific is written here.  Bucket row lists are small host-side
+// metadata and are built by the caller from the scale tensor (mpserve_b200/encoder.py).
+#include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_run_length_encode.cuh>
+#include <cub/device/device_scan.cuh>
+
+#include <string.h>
+
+#include "mps_common.cuh"
+
+namespace mps {
+
+// ------------------------------------------------------------------------------------------------
+// build state: where things live inside the caller's workspace (host-side POD, opaque to callers)
+// ------------------------------------------------------------------------------------------------
+struct BuildState {
+    int64_t numel, n, m;
+    int64_t N;                 // distinct (context, symbol) pairs
+    int64_t G;                 // contexts
+    int32_t L, variant;
+    uint8_t* ws;               // device workspace base
+    size_t ws_bytes;
+    // offsets (bytes) into ws
+    size_t o_items;            // uint64 [N]  scale<<32 | ctx<<16 | sym, ascending
+    size_t o_counts;           // int32  [N]
+    size_t o_ctx_ofs;          // int32  [G+1] first item of each context
+    size_t o_ctx_key;          // uint32 [G]   scale<<16 | ctx
+    size_t o_perm;             // int32  [N]   items of each context ordered by (count, sym)
+    size_t o_enc;              // uint32 [N]   len<<16 | code of each item, 0 = not coded (ESC'd)
+    size_t o_esc;              // uint32 [G]   len<<16 | code of the context's ESC code (0: none)
+    size_t o_escsym;           // uint16 [G]
+    size_t o_scratch;          // start of the reusable scratch area
+    size_t scratch_bytes;
+    int32_t* d_flag;           // device error flag (first word of ws)
+};
+static_assert(sizeof(BuildState) <= 256, "mps_build_state is 256 bytes");
+
+static inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+enum { V_FP8 = 0, V_AWQ_BUCKET = 1, V_AWQ_BYSCALE = 2, V_AWQ_SHARED = 3 };
+
+// ------------------------------------------------------------------------------------------------
+// analyze
+// ------------------------------------------------------------------------------------------------
+// scale_mode: 0 scalar, 1 per row, 2 two-dimensional blocks [nb0, nb1] of sb0 x sb1 elements
+__global__ void make_composites_kernel(const uint16_t* __restrict__ sym, const uint8_t* __restrict__ ctx,
+                                       const uint16_t* __restrict__ scales, int scale_mode, long long m, long long nb1,
+                                       long long sb0, long long sb1, uint32_t ctx_mask, long long numel,
+                                       unsigned long long* __restrict__ comp) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += (long long)gridDim.x * blockDim.x) {
+        long long sidx = 0;
+        if (scale_mode != 0) {
+            const long long r = i / m;
+            sidx = (scale_mode == 1) ? r : (r / sb0) * nb1 + (i - r * m) / sb1;
+        }
+        comp[i] = ((unsigned long long)scales[sidx] << 32) | ((unsigned long long)(ctx[i] & ctx_mask) << 16) | sym[i];
+    }
+}
+
+__global__ void context_heads_kernel(const unsigned long long* __restrict__ items, long long N, int* __restrict__ head) {
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < N; j += (long long)gridDim.x * blockDim.x)
+        head[j] = (j == 0 || (items[j] >> 16) != (items[j - 1] >> 16)) ? 1 : 0;
+}
+
+// cid = inclusive scan of head; context g starts where head is set
+__global__ void context_offsets_kernel(const unsigned long long* __restrict__ items, const int* __restrict__ head,
+                                       const int* __restrict__ cid, long long N, int* __restrict__ ctx_ofs,
+                                       uint32_t* __restrict__ ctx_key) {
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < N; j += (long long)gridDim.x * blockDim.x) {
+        if (head[j]) {
+            const int g = cid[j] - 1;
+            ctx_ofs[g] = (int)j;
+            ctx_key[g] = (uint32_t)(items[j] >> 16);
+        }
+        if (j == N - 1) ctx_ofs[cid[j]] = (int)N;
+    }
+}
+
+__global__ void item_sort_keys_kernel(const unsigned long long* __restrict__ items, const int* __restrict__ counts,
+                                      const int* __restrict__ cid, long long N, unsigned long long* __restrict__ k1,
+                                      int* __restrict__ v, uint32_t* __restrict__ ctx_of_item) {
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < N; j += (long long)gridDim.x * blockDim.x) {
+        k1[j] = ((unsigned long long)(uint32_t)counts[j] << 16) | (items[j] & 0xFFFFull);
+        v[j] = (int)j;
+        ctx_of_item[j] = (uint32_t)(cid[j] - 1);
+    }
+}
+
+__global__ void gather_u32_kernel(const uint32_t* __restrict__ src, const int* __restrict__ idx, long long N,
+                                  uint32_t* __restrict__ dst) {
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < N; j += (long long)gridDim.x * blockDim.x)
+        dst[j] = src[idx[j]];
+}
+
+static int grid_for(long long n, int threads = 256) {
+    long long b = (n + threads - 1) / threads;
+    if (b > 148LL * 32) b = 148LL * 32;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+}  // namespace mps
+
+namespace mps {
+
+// ------------------------------------------------------------------------------------------------
+// codebooks: one thread per context, thread-private arrays interleaved in global scratch
+// ------------------------------------------------------------------------------------------------
+struct CbScratch {      // arrays of a chunk of `chunk` contexts; element i of slot s at [i * chunk + s]
+    unsigned long long* w;    // [TS]   weights of the final item list (ascending)
+    uint16_t* sym;            // [TS]
+    int* src;                 // [TS]   index into the histogram items, -1 for the ESC item
+    unsigned long long* cur;  // [KEEP] package-merge list of the current level
+    unsigned long long* nxt;  // [KEEP]
+    uint8_t* flag;            // [L * KEEP] 1 where the level's list holds a leaf
+    uint8_t* len;             // [TS]
+    int chunk;
+};
+
+__device__ __forceinline__ void set_nibble(uint8_t* packed, long long idx, uint32_t v) {
+    uint8_t b = packed[idx >> 1];
+    b = (idx & 1) ? (uint8_t)((b & 0x0F) | (v << 4)) : (uint8_t)((b & 0xF0) | (v & 0x0F));
+    packed[idx >> 1] = b;
+}
+
+// Length-limited code lengths of n >= 2 ascending weights (build_huffman.cu:46-118), by counting
+// leaves in list prefixes instead of walking package trees: the items chosen at every level are a
+// prefix of that level's list, because packages pair consecutive items from the front and a leaf
+// wins a tie when lists are merged.
+__device__ bool package_merge_device(const CbScratch& S, int s, int n, int L) {
+#define AT(arr, i) arr[(long long)(i) * S.chunk + s]
+    const int K = 2 * (n - 1), keep = 2 * K;
+    const int KEEP = 4 * ((1 << L) - 1);
+    int cur_n = n;
+    for (int i = 0; i < n; ++i) { AT(S.cur, i) = AT(S.w, i); AT(S.flag, i) = 1; }
+    unsigned long long* cur = S.cur;
+    unsigned long long* nxt = S.nxt;
+    for (int p = 0; p < L - 1; ++p) {
+        const int trunc = cur_n < keep ? cur_n : keep;
+        const int npk = trunc / 2;
+        uint8_t* fl = S.flag + (long long)(p + 1) * KEEP * S.chunk;
+        int i = 0, j = 0, o = 0;
+        while (o < keep && (i < n || j < npk)) {
+            bool leaf;
+            unsigned long long pw = 0;
+            if (j < npk) pw = AT(cur, 2 * j) + AT(cur, 2 * j + 1);
+            if (i < n && j < npk) leaf = AT(S.w, i) <= pw;
+            else leaf = (i < n);
+            if (leaf) { AT(nxt, o) = AT(S.w, i); ++i; } else { AT(nxt, o) = pw; ++j; }
+            AT(fl, o) = leaf ? 1 : 0;
+            ++o;
+        }
+        cur_n = o;
+        unsigned long long* t = cur; cur = nxt; nxt = t;
+    }
+    if (cur_n < K) return false;
+    for (int i = 0; i < n; ++i) AT(S.len, i) = 0;
+    int take = K;
+    for (int lvl = L - 1; lvl >= 0 && take > 0; --lvl) {
+        const uint8_t* fl = S.flag + (long long)lvl * KEEP * S.chunk;
+        int c = 0;
+        for (int i = 0; i < take; ++i) c += AT(fl, i);
+        for (int i = 0; i < c; ++i) AT(S.len, i) = (uint8_t)(AT(S.len, i) + 1);
+        take = 2 * (take - c);
+    }
+    return true;
+}
+
+// variant: V_FP8 or V_AWQ_BUCKET.  Tables are written at index g (contexts in ascending key order).
+__global__ void codebook_kernel(const unsigned long long* __restrict__ items, const int* __restrict__ counts,
+                                const int* __restrict__ ctx_ofs, const int* __restrict__ perm, long long g0, long long g1,
+                                int L, int variant, CbScratch S, uint16_t* __restrict__ out_syms,
+                                uint8_t* __restrict__ out_lens, uint32_t* __restrict__ enc, uint32_t* __restrict__ esc,
+                                uint16_t* __restrict__ escsym, int* __restrict__ err) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    const long long g = g0 + s;
+    if (g >= g1 || s >= S.chunk) return;
+    const int TS = 1 << L;
+    const int a = ctx_ofs[g], b = ctx_ofs[g + 1], cnt = b - a;
+    uint16_t* tsym = out_syms + g * TS;
+    uint8_t* tlen = out_lens + g * (TS / 2);
+    esc[g] = 0;
+    escsym[g] = 0;
+    if (cnt <= 0) return;
+    if (cnt == 1) {  // single symbol: length 1, code 0, every slot (build_huffman.cu:464-472)
+        const uint16_t sy = (uint16_t)(items[a] & 0xFFFF);
+        for (int i = 0; i < TS; ++i) tsym[i] = sy;
+        for (int i = 0; i < TS / 2; ++i) tlen[i] = 0x11;
+        enc[a] = (1u << 16);
+        return;
+    }
+    int n = cnt;
+    bool use_esc = false;
+    uint16_t esc_sym = 0;
+    int esc_pos = -1;
+    if (cnt > TS) {
+        // keep the TS-1 most frequent (ties: smaller symbol first), fold the rest into one ESC item
+        use_esc = true;
+        const int keepk = TS - 1;
+        const int p = b - keepk;                       // lowest kept position if there were no ties
+        const int fb = counts[perm[p]];                // count of the boundary class
+        int lo = p, hi = p;
+        while (lo > a && counts[perm[lo - 1]] == fb) --lo;
+        while (hi < b && counts[perm[hi]] == fb) ++hi;  // class fb is perm[lo, hi)
+        const int r = keepk - (b - hi);                // how many of the class are kept: its first r
+        long long esc_w = 0;
+        int seen = 0;
+        uint32_t cand = 0;
+        bool cand_done = false;
+        for (int j = a; j < b; ++j) {                  // histogram order = ascending symbol
+            const int c = counts[j];
+            const bool kept = c > fb || (c == fb && seen < r);
+            if (c == fb) ++seen;
+            const uint32_t sy = (uint32_t)(items[j] & 0xFFFF);
+            if (!kept) { esc_w += c; enc[j] = 0; }
+            if (!cand_done) {
+                if (kept && sy == cand) ++cand;
+                else if (sy > cand) cand_done = true;
+            }
+        }
+        esc_sym = (uint16_t)(cand <= 0xFFFFu ? cand : 0xFFFFu);
+        int esc_i = (int)esc_w;                        // the reference accumulates in int
+        if (variant != V_FP8 && esc_i <= 0) esc_i = 1;
+        // final list, ascending by (weight, symbol): perm[lo, lo+r), perm[hi, b), ESC inserted in order
+        n = 0;
+        bool placed = false;
+        for (int q = 0; q < keepk; ++q) {
+            const int j = perm[q < r ? lo + q : hi + (q - r)];
+            const unsigned long long w = (unsigned long long)(uint32_t)counts[j];
+            const uint16_t sy = (uint16_t)(items[j] & 0xFFFF);
+            if (!placed && ((unsigned long long)(uint32_t)esc_i < w || ((unsigned long long)(uint32_t)esc_i == w && esc_sym < sy))) {
+                AT(S.w, n) = (unsigned long long)(uint32_t)esc_i; AT(S.sym, n) = esc_sym; AT(S.src, n) = -1; esc_pos = n; ++n;
+                placed = true;
+            }
+            AT(S.w, n) = w; AT(S.sym, n) = sy; AT(S.src, n) = j; ++n;
+        }
+        if (!placed) { AT(S.w, n) = (unsigned long long)(uint32_t)esc_i; AT(S.sym, n) = esc_sym; AT(S.src, n) = -1; esc_pos = n; ++n; }
+    } else {
+        for (int q = 0; q < cnt; ++q) {
+            const int j = perm[a + q];
+            AT(S.w, q) = (unsigned long long)(uint32_t)counts[j];
+            AT(S.sym, q) = (uint16_t)(items[j] & 0xFFFF);
+            AT(S.src, q) = j;
+        }
+    }
+    if (!package_merge_device(S, s, n, L)) { atomicExch(err, 2); return; }
+    if (use_esc && variant == V_AWQ_BUCKET) AT(S.len, esc_pos) = (uint8_t)L;  // ESC code forced to L bits (:1812-1816)
+
+    // canonical codes handed out in item order within each length (build_huffman.cu:171-203)
+    uint32_t next_code[17];
+    {
+        int bl[17];
+        for (int i = 0; i < 17; ++i) bl[i] = 0;
+        for (int i = 0; i < n; ++i) bl[AT(S.len, i)]++;
+        uint32_t code = 0;
+        next_code[0] = 0;
+        for (int bits = 1; bits < 17; ++bits) { code = (code + (uint32_t)bl[bits - 1]) << 1; next_code[bits] = code; }
+    }
+    for (int i = 0; i < n; ++i) {
+        const int len = AT(S.len, i);
+        const uint32_t code = next_code[len]++;
+        const uint16_t sy = AT(S.sym, i);
+        const int src = AT(S.src, i);
+        const uint32_t packed = ((uint32_t)len << 16) | code;
+        if (src >= 0) enc[src] = packed; else { esc[g] = packed; escsym[g] = sy; }
+        const uint32_t nib = (variant == V_FP8 && src < 0) ? (uint32_t)(len | 8) : (uint32_t)len;
+        const uint32_t base = code << (L - len), fill = 1u << (L - len);
+        for (uint32_t t = 0; t < fill; ++t) {
+            const uint32_t idx = base + t;
+            if (idx < (uint32_t)TS) { tsym[idx] = sy; set_nibble(tlen, idx, nib); }
+        }
+    }
+    if (use_esc && variant == V_AWQ_BUCKET) {  // every slot that shows the ESC symbol is marked 15 (:1822-1829)
+        for (int i = 0; i < TS; ++i)
+            if (tsym[i] == esc_sym) set_nibble(tlen, i, 15u);
+    }
+#undef AT
+}
+
+}  // namespace mps
+
+namespace mps {
+
+// ------------------------------------------------------------------------------------------------
+// bucket tables, layout, emit (rectangular buckets: FP8 and AWQ bucket builders)
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ int find_u32(const uint32_t* __restrict__ a, int n, uint32_t key) {
+    int lo = 0, hi = n - 1;
+    while (lo <= hi) {
+        const int mid = (lo + hi) >> 1;
+        const uint32_t v = a[mid];
+        if (v == key) return mid;
+        if (v < key) lo = mid + 1; else hi = mid - 1;
+    }
+    return -1;
+}
+
+// context -> table id of every bucket (build_huffman.cu:737-746)
+__global__ void bucket_table_kernel(const uint32_t* __restrict__ ctx_key, int G, const uint16_t* __restrict__ bucket_scale,
+                                    long long B, int nctx, int32_t* __restrict__ out) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < B * nctx; i += (long long)gridDim.x * blockDim.x) {
+        const long long b = i / nctx;
+        const uint32_t c = (uint32_t)(i - b * nctx);
+        out[i] = find_u32(ctx_key, G, ((uint32_t)bucket_scale[b] << 16) | c);
+    }
+}
+
+// first-appearance list of a bucket's tables and context -> position in it (build_huffman.cu:748-783)
+__global__ void bucket_unique_kernel(const int32_t* __restrict__ bt, long long B, int32_t* __restrict__ U,
+                                     int32_t* __restrict__ uniq, int16_t* __restrict__ uidx) {
+    for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < B; b += (long long)gridDim.x * blockDim.x) {
+        int32_t u = 0;
+        for (int i = 0; i < 256; ++i) { uniq[b * 256 + i] = -1; uidx[b * 256 + i] = -1; }
+        for (int i = 0; i < 256; ++i) {
+            const int32_t gid = bt[b * 256 + i];
+            if (gid < 0) continue;
+            int32_t found = -1;
+            for (int32_t j = 0; j < u; ++j) if (uniq[b * 256 + j] == gid) { found = j; break; }
+            if (found < 0) { uniq[b * 256 + u] = gid; found = u++; }
+            uidx[b * 256 + i] = (int16_t)found;
+        }
+        U[b] = u;
+    }
+}
+
+struct RectGeom {
+    const uint16_t* sym;              // [n*m] BF16 bit patterns
+    const uint8_t* ctx;               // [n*m]
+    const int32_t* bucket_table;      // [B, nctx]
+    const int32_t* col_start;         // [B]
+    const int32_t* col_len;           // [B]
+    const int32_t* row_ofs;           // [B+1]
+    const int32_t* rows;              // row lists
+    long long B, m;
+    int k, nctx;
+    uint32_t ctx_mask;
+};
+
+struct CodeBook {
+    const unsigned long long* items;
+    const int* ctx_ofs;
+    const uint32_t* enc;
+    const uint32_t* esc;
+    const uint16_t* escsym;
+};
+
+// (code, length) of one element, ESC expansion included: returns total bits, code(s) via out params
+__device__ __forceinline__ int element_code(const CodeBook& cb, int gid, uint32_t sym, uint32_t& code, int& len,
+                                            bool& raw) {
+    const int a = cb.ctx_ofs[gid], b = cb.ctx_ofs[gid + 1];
+    int lo = a, hi = b - 1, j = -1;
+    while (lo <= hi) {
+        const int mid = (lo + hi) >> 1;
+        const uint32_t v = (uint32_t)(cb.items[mid] & 0xFFFF);
+        if (v == sym) { j = mid; break; }
+        if (v < sym) lo = mid + 1; else hi = mid - 1;
+    }
+    raw = false;
+    if (j < 0) return -1;
+    uint32_t lc = cb.enc[j];
+    if (lc == 0) {                       // not in the codebook: ESC code, then the raw 16 bits ...
+        lc = cb.esc[gid];
+        if (lc == 0) return -1;
+        raw = (sym != cb.escsym[gid]);   // ... unless the symbol equals the synthetic ESC symbol, which the
+    }                                    // reference's encoder map resolves to the bare ESC code
+    code = lc & 0xFFFF;
+    len = (int)(lc >> 16);
+    return len + (raw ? 16 : 0);
+}
+
+template <bool EMIT>
+__global__ void rect_walk_kernel(RectGeom g, CodeBook cb, const uint32_t* __restrict__ startbit,
+                                 const long long* __restrict__ bit_base, uint32_t* __restrict__ bits_out,
+                                 unsigned long long* __restrict__ bitstream, int* __restrict__ err) {
+    const long long total_threads = g.B * g.k;
+    for (long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x; id < total_threads; id += (long long)gridDim.x * blockDim.x) {
+        const long long b = id / g.k;
+        const int t = (int)(id - b * g.k);
+        const int row_a = g.row_ofs[b];
+        const long long nrows = g.row_ofs[b + 1] - row_a;
+        const long long col_len = g.col_len[b], col_start = g.col_start[b];
+        const long long total = nrows * col_len;
+        long long k_eff = total < 1 ? 1 : total;
+        if (k_eff > g.k) k_eff = g.k;
+        if (t >= k_eff) { if (!EMIT) bits_out[id] = 0; continue; }
+        const int32_t* bt = g.bucket_table + b * g.nctx;
+        // output cursor (emit)
+        long long w = 0; int fill = 0; unsigned long long acc = 0;
+        if (EMIT) {
+            const long long bitpos = bit_base[b] + (long long)startbit[b * ((long long)g.k + 1) + t];
+            w = bitpos >> 6; fill = (int)(bitpos & 63);
+        }
+        unsigned long long bits = 0;
+        long long rr = t / col_len, cc = t - rr * col_len;
+        for (long long e = t; e < total; e += k_eff) {
+            const long long i = (long long)g.rows[row_a + rr] * g.m + col_start + cc;
+            const int gid = bt[g.ctx[i] & g.ctx_mask];
+            uint32_t code = 0; int len = 0; bool raw = false;
+            const uint32_t sym = g.sym[i];
+            const int nb = (gid >= 0) ? element_code(cb, gid, sym, code, len, raw) : -1;
+            if (nb < 0) { atomicExch(err, 3); break; }
+            bits += (unsigned long long)nb;
+            if (EMIT) {
+                // the code, then (after an ESC) the 16 raw bits, MSB first
+                unsigned long long v = raw ? (((unsigned long long)code << 16) | sym) : code;
+                int left = nb;
+                while (left > 0) {
+                    const int room = 64 - fill;
+                    const int take = left < room ? left : room;
+                    const unsigned long long part = (v >> (left - take)) & ((take >= 64) ? ~0ull : ((1ull << take) - 1ull));
+                    acc |= part << (room - take);
+                    fill += take; left -= take;
+                    if (fill == 64) { atomicOr(&bitstream[w], acc); ++w; acc = 0; fill = 0; }
+                }
+            }
+            cc += k_eff;
+            while (cc >= col_len) { cc -= col_len; ++rr; }
+        }
+        if (EMIT) { if (acc) atomicOr(&bitstream[w], acc); }
+        else bits_out[id] = (uint32_t)bits;
+    }
+}
+
+// per bucket: start bit of every sub-stream relative to the bucket (build_huffman.cu:869-879)
+__global__ void rect_starts_kernel(const uint32_t* __restrict__ bits, const int32_t* __restrict__ row_ofs,
+                                   const int32_t* __restrict__ col_len, long long B, int k, uint32_t* __restrict__ startbit,
+                                   unsigned long long* __restrict__ bucket_bits) {
+    for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < B; b += (long long)gridDim.x * blockDim.x) {
+        const long long total = (long long)(row_ofs[b + 1] - row_ofs[b]) * col_len[b];
+        long long k_eff = total < 1 ? 1 : total;
+        if (k_eff > k) k_eff = k;
+        uint32_t* st = startbit + b * ((long long)k + 1);
+        unsigned long long rel = 0;
+        st[0] = 0;
+        for (long long t = 0; t < k_eff; ++t) { rel += bits[b * k + t]; st[t + 1] = (uint32_t)rel; }
+        for (long long t = k_eff + 1; t <= k; ++t) st[t] = st[k_eff];
+        bucket_bits[b] = rel;
+    }
+}
+
+// 64-bit aligned start of every bucket, [B] = end of the stream (build_huffman.cu:811-817, 918)
+__global__ void bucket_bases_kernel(const unsigned long long* __restrict__ bucket_bits, long long B,
+                                    long long* __restrict__ bit_base) {
+    if (blockIdx.x != 0 || threadIdx.x != 0) return;
+    long long pos = 0;
+    for (long long b = 0; b < B; ++b) {
+        if (pos & 63) pos = (pos + 63) & ~63LL;
+        bit_base[b] = pos;
+        pos += (long long)bucket_bits[b];
+    }
+    bit_base[B] = pos;
+}
+
+__global__ void table_keys_kernel(const uint32_t* __restrict__ ctx_key, long long G, uint16_t* __restrict__ tscale,
+                                  uint16_t* __restrict__ tctx) {
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < G; g += (long long)gridDim.x * blockDim.x) {
+        tscale[g] = (uint16_t)(ctx_key[g] >> 16);
+        tctx[g] = (uint16_t)(ctx_key[g] & 0xFFFF);
+    }
+}
+
+}  // namespace mps
+
+// ------------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------------
+using namespace mps;
+
+namespace {
+
+constexpr size_t kCubTempBytes = 96ull << 20;      // device-wide primitives' temporary storage
+constexpr size_t kCodebookScratch = 160ull << 20;  // interleaved per-context arrays of the codebook pass
+
+struct Carver {
+    uint8_t* base; size_t off, cap;
+    template <typename T> T* take(size_t count) {
+        off = align_up(off);
+        T* p = reinterpret_cast<T*>(base + off);
+        off += count * sizeof(T);
+        return p;
+    }
+    bool ok() const { return off <= cap; }
+};
+
+inline BuildState* state_of(mps_build_state* s) { return reinterpret_cast<BuildState*>(s); }
+
+size_t codebook_slot_bytes(int L) {
+    const size_t TS = 1ull << L, KEEP = 4 * (TS - 1);
+    return TS * (8 + 2 + 4 + 1) + KEEP * 16 + (size_t)L * KEEP;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t mps_build_workspace_bytes(int64_t numel, int64_t substreams) {
+    if (numel < 0) numel = 0;
+    if (substreams < numel) substreams = numel;
+    return 256 + (size_t)numel * 34 + (size_t)numel * 40 + (size_t)substreams * 4 + kCubTempBytes + kCodebookScratch +
+           (1ull << 20);
+}
+
+int mps_build_analyze(mps_build_state* state, const uint16_t* bf16_bits, const uint8_t* ctx_bytes,
+                      const uint16_t* scales_u16, int32_t scale_mode, int64_t nb1, int64_t sb0, int64_t sb1, int64_t n,
+                      int64_t m, int32_t variant, int64_t max_len, void* workspace, size_t workspace_bytes, void* stream,
+                      int64_t* num_tables_out, int64_t* num_items_out) {
+    if (!state || !bf16_bits || !ctx_bytes || !scales_u16 || !workspace || !num_tables_out || !num_items_out) {
+        set_error("mps_build_analyze: null argument");
+        return MPS_ERR_INVALID;
+    }
+    if (n <= 0 || m <= 0) { set_error("bf16_params shape must be non-empty"); return MPS_ERR_INVALID; }
+    if (variant != V_FP8 && variant != V_AWQ_BUCKET) { set_error("this builder variant is not implemented on the GPU yet"); return MPS_ERR_UNSUPPORTED; }
+    if (max_len <= 0 || max_len > 15) { set_error("max_len must be in [1, 15]"); return MPS_ERR_INVALID; }
+    if (scale_mode < 0 || scale_mode > 2 || (scale_mode == 2 && (nb1 <= 0 || sb0 <= 0 || sb1 <= 0))) {
+        set_error("unsupported scales layout");
+        return MPS_ERR_INVALID;
+    }
+    const int64_t numel = n * m;
+    if (numel >= (1LL << 31)) { set_error("tensors of 2^31 elements or more are not supported by the builder"); return MPS_ERR_UNSUPPORTED; }
+    if (workspace_bytes < mps_build_workspace_bytes(numel, numel)) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    BuildState& S = *state_of(state);
+    memset(&S, 0, sizeof(S));
+    S.numel = numel; S.n = n; S.m = m; S.L = (int32_t)max_len; S.variant = variant;
+    S.ws = static_cast<uint8_t*>(workspace); S.ws_bytes = workspace_bytes;
+    Carver C{S.ws, 256, workspace_bytes};
+    S.d_flag = reinterpret_cast<int32_t*>(S.ws);
+    auto* items = C.take<unsigned long long>(numel);  S.o_items = (uint8_t*)items - S.ws;
+    auto* counts = C.take<int>(numel);                S.o_counts = (uint8_t*)counts - S.ws;
+    auto* ctx_ofs = C.take<int>(numel + 1);           S.o_ctx_ofs = (uint8_t*)ctx_ofs - S.ws;
+    auto* ctx_key = C.take<uint32_t>(numel);          S.o_ctx_key = (uint8_t*)ctx_key - S.ws;
+    auto* perm = C.take<int>(numel);                  S.o_perm = (uint8_t*)perm - S.ws;
+    auto* enc = C.take<uint32_t>(numel);              S.o_enc = (uint8_t*)enc - S.ws;
+    auto* esc = C.take<uint32_t>(numel);              S.o_esc = (uint8_t*)esc - S.ws;
+    auto* escsym = C.take<uint16_t>(numel);           S.o_escsym = (uint8_t*)escsym - S.ws;
+    C.off = align_up(C.off);
+    S.o_scratch = C.off; S.scratch_bytes = workspace_bytes - C.off;
+    // scratch of this call
+    auto* comp_a = C.take<unsigned long long>(numel);
+    auto* comp_b = C.take<unsigned long long>(numel);
+    auto* d_runs = C.take<long long>(4);
+    void* cub_tmp = C.take<uint8_t>(kCubTempBytes);
+    if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
+
+    MPS_CUDA_TRY(cudaMemsetAsync(S.d_flag, 0, 256, st));
+    const uint32_t ctx_mask = (variant == V_FP8) ? 0xFFu : 0x0Fu;
+    make_composites_kernel<<<grid_for(numel), 256, 0, st>>>(bf16_bits, ctx_bytes, scales_u16, scale_mode, m, nb1, sb0, sb1,
+                                                            ctx_mask, numel, comp_a);
+    MPS_CUDA_TRY(cudaGetLastError());
+    size_t need = 0;
+    MPS_CUDA_TRY(cub::DeviceRadixSort::SortKeys(nullptr, need, comp_a, comp_b, (int)numel, 0, 48, st));
+    if (need > kCubTempBytes) { set_error("sort temporary storage exceeds the reserved %zu bytes", kCubTempBytes); return MPS_ERR_WORKSPACE; }
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceRadixSort::SortKeys(cub_tmp, need, comp_a, comp_b, (int)numel, 0, 48, st));
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceRunLengthEncode::Encode(cub_tmp, need, comp_b, items, counts, d_runs, (int)numel, st));
+    long long N = 0;
+    MPS_CUDA_TRY(cudaMemcpyAsync(&N, d_runs, sizeof(N), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    S.N = N;
+
+    // contexts: heads -> ids -> offsets and keys
+    C.off = S.o_scratch;  // the composites are no longer needed
+    auto* head = C.take<int>(N);
+    auto* cid = C.take<int>(N);
+    auto* k1 = C.take<unsigned long long>(N);
+    auto* k1o = C.take<unsigned long long>(N);
+    auto* v = C.take<int>(N);
+    auto* vo = C.take<int>(N);
+    auto* ci = C.take<uint32_t>(N);
+    auto* cio = C.take<uint32_t>(N);
+    cub_tmp = C.take<uint8_t>(kCubTempBytes);
+    if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
+    context_heads_kernel<<<grid_for(N), 256, 0, st>>>(items, N, head);
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceScan::InclusiveSum(cub_tmp, need, head, cid, (int)N, st));
+    context_offsets_kernel<<<grid_for(N), 256, 0, st>>>(items, head, cid, N, ctx_ofs, ctx_key);
+    int G = 0;
+    MPS_CUDA_TRY(cudaMemcpyAsync(&G, cid + (N - 1), sizeof(int), cudaMemcpyDeviceToHost, st));
+    // items of every context ordered by (count, symbol): sort by that key, then stably by context
+    item_sort_keys_kernel<<<grid_for(N), 256, 0, st>>>(items, counts, cid, N, k1, v, ci);
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceRadixSort::SortPairs(cub_tmp, need, k1, k1o, v, vo, (int)N, 0, 48, st));
+    gather_u32_kernel<<<grid_for(N), 256, 0, st>>>(ci, vo, N, cio);
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceRadixSort::SortPairs(cub_tmp, need, cio, ci, vo, perm, (int)N, 0, 32, st));
+    MPS_CUDA_TRY(cudaGetLastError());
+    MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    S.G = G;
+    *num_tables_out = G;
+    *num_items_out = N;
+    return MPS_OK;
+}
+
+int mps_build_codebooks(mps_build_state* state, uint16_t* decode_syms_u16, uint8_t* decode_lens_u8,
+                        uint16_t* table_scale_u16, uint16_t* table_ctx_u16, void* stream) {
+    if (!state || !decode_syms_u16 || !decode_lens_u8 || !table_scale_u16 || !table_ctx_u16) {
+        set_error("mps_build_codebooks: null argument");
+        return MPS_ERR_INVALID;
+    }
+    BuildState& S = *state_of(state);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int L = S.L;
+    const size_t TS = 1ull << L, KEEP = 4 * (TS - 1);
+    const size_t slot = codebook_slot_bytes(L);
+    long long chunk = (long long)((kCodebookScratch - (1 << 16)) / slot);
+    if (chunk > S.G) chunk = S.G;
+    if (chunk < 1) { set_error("codebook scratch too small for max_len=%d", L); return MPS_ERR_WORKSPACE; }
+    chunk = (chunk / 32) * 32 > 0 ? (chunk / 32) * 32 : chunk;
+    Carver C{S.ws, S.o_scratch, S.ws_bytes};
+    CbScratch cs;
+    cs.chunk = (int)chunk;
+    cs.w = C.take<unsigned long long>(TS * chunk);
+    cs.cur = C.take<unsigned long long>(KEEP * chunk);
+    cs.nxt = C.take<unsigned long long>(KEEP * chunk);
+    cs.src = C.take<int>(TS * chunk);
+    cs.sym = C.take<uint16_t>(TS * chunk);
+    cs.flag = C.take<uint8_t>((size_t)L * KEEP * chunk);
+    cs.len = C.take<uint8_t>(TS * chunk);
+    if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
+    auto* items = reinterpret_cast<unsigned long long*>(S.ws + S.o_items);
+    auto* counts = reinterpret_cast<int*>(S.ws + S.o_counts);
+    auto* ctx_ofs = reinterpret_cast<int*>(S.ws + S.o_ctx_ofs);
+    auto* ctx_key = reinterpret_cast<uint32_t*>(S.ws + S.o_ctx_key);
+    auto* perm = reinterpret_cast<int*>(S.ws + S.o_perm);
+    auto* enc = reinterpret_cast<uint32_t*>(S.ws + S.o_enc);
+    auto* esc = reinterpret_cast<uint32_t*>(S.ws + S.o_esc);
+    auto* escsym = reinterpret_cast<uint16_t*>(S.ws + S.o_escsym);
+    MPS_CUDA_TRY(cudaMemsetAsync(decode_syms_u16, 0, (size_t)S.G * TS * 2, st));
+    MPS_CUDA_TRY(cudaMemsetAsync(decode_lens_u8, 0, (size_t)S.G * TS / 2, st));
+    for (long long g0 = 0; g0 < S.G; g0 += chunk) {
+        const long long g1 = (g0 + chunk < S.G) ? g0 + chunk : S.G;
+        codebook_kernel<<<(int)((g1 - g0 + 63) / 64), 64, 0, st>>>(items, counts, ctx_ofs, perm, g0, g1, L, S.variant, cs,
+                                                                    decode_syms_u16, decode_lens_u8, enc, esc, escsym,
+                                                                    S.d_flag);
+    }
+    table_keys_kernel<<<grid_for(S.G), 256, 0, st>>>(ctx_key, S.G, table_scale_u16, table_ctx_u16);
+    MPS_CUDA_TRY(cudaGetLastError());
+    int flag = 0;
+    MPS_CUDA_TRY(cudaMemcpyAsync(&flag, S.d_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    if (flag == 2) { set_error("Internal error: not enough packages"); return (int)cudaErrorUnknown; }
+    return MPS_OK;
+}
+
+int mps_build_bucket_table(mps_build_state* state, const uint16_t* bucket_scale_u16, int64_t num_buckets,
+                           int32_t* bucket_table_i32, void* stream) {
+    if (!state || !bucket_scale_u16 || !bucket_table_i32 || num_buckets < 0) { set_error("mps_build_bucket_table: bad argument"); return MPS_ERR_INVALID; }
+    BuildState& S = *state_of(state);
+    const int nctx = (S.variant == V_FP8) ? 256 : 16;
+    auto* ctx_key = reinterpret_cast<uint32_t*>(S.ws + S.o_ctx_key);
+    if (num_buckets == 0) return MPS_OK;
+    bucket_table_kernel<<<grid_for(num_buckets * nctx), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        ctx_key, (int)S.G, bucket_scale_u16, num_buckets, nctx, bucket_table_i32);
+    MPS_CUDA_TRY(cudaGetLastError());
+    return MPS_OK;
+}
+
+int mps_build_bucket_unique(const int32_t* bucket_table_i32, int64_t num_buckets, int32_t* bucket_U_i32,
+                            int32_t* bucket_unique_gid_i32, int16_t* bucket_fp8_uidx_i16, void* stream) {
+    if (!bucket_table_i32 || !bucket_U_i32 || !bucket_unique_gid_i32 || !bucket_fp8_uidx_i16 || num_buckets < 0) {
+        set_error("mps_build_bucket_unique: bad argument");
+        return MPS_ERR_INVALID;
+    }
+    if (num_buckets == 0) return MPS_OK;
+    bucket_unique_kernel<<<grid_for(num_buckets, 64), 64, 0, static_cast<cudaStream_t>(stream)>>>(
+        bucket_table_i32, num_buckets, bucket_U_i32, bucket_unique_gid_i32, bucket_fp8_uidx_i16);
+    MPS_CUDA_TRY(cudaGetLastError());
+    return MPS_OK;
+}
+
+static int rect_common(mps_build_state* state, const uint16_t* bf16_bits, const uint8_t* ctx_bytes,
+                       const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                       const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                       const int32_t* row_indices_i32, int64_t num_buckets, int32_t k, RectGeom* g, CodeBook* cb) {
+    if (!state || !bf16_bits || !ctx_bytes || !bucket_table_i32 || !bucket_col_start_i32 || !bucket_col_len_i32 ||
+        !bucket_row_offsets_i32 || !row_indices_i32 || num_buckets < 0 || k <= 0 || k > 1024) {
+        set_error("sidecar layout: bad argument");
+        return MPS_ERR_INVALID;
+    }
+    BuildState& S = *state_of(state);
+    g->sym = bf16_bits; g->ctx = ctx_bytes; g->bucket_table = bucket_table_i32; g->col_start = bucket_col_start_i32;
+    g->col_len = bucket_col_len_i32; g->row_ofs = bucket_row_offsets_i32; g->rows = row_indices_i32;
+    g->B = num_buckets; g->m = S.m; g->k = k; g->nctx = (S.variant == V_FP8) ? 256 : 16;
+    g->ctx_mask = (S.variant == V_FP8) ? 0xFFu : 0x0Fu;
+    cb->items = reinterpret_cast<unsigned long long*>(S.ws + S.o_items);
+    cb->ctx_ofs = reinterpret_cast<int*>(S.ws + S.o_ctx_ofs);
+    cb->enc = reinterpret_cast<uint32_t*>(S.ws + S.o_enc);
+    cb->esc = reinterpret_cast<uint32_t*>(S.ws + S.o_esc);
+    cb->escsym = reinterpret_cast<uint16_t*>(S.ws + S.o_escsym);
+    return MPS_OK;
+}
+
+int mps_build_rect_layout(mps_build_state* state, const uint16_t* bf16_bits, const uint8_t* ctx_bytes,
+                          const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                          const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                          const int32_t* row_indices_i32, int64_t num_buckets, int32_t k,
+                          uint32_t* bucket_thread_startbit_u32, int64_t* bucket_bit_base_i64, void* stream,
+                          int64_t* total_bits_out) {
+    RectGeom g; CodeBook cb;
+    int rc = rect_common(state, bf16_bits, ctx_bytes, bucket_table_i32, bucket_col_start_i32, bucket_col_len_i32,
+                         bucket_row_offsets_i32, row_indices_i32, num_buckets, k, &g, &cb);
+    if (rc) return rc;
+    if (!bucket_thread_startbit_u32 || !bucket_bit_base_i64 || !total_bits_out) { set_error("sidecar layout: null output"); return MPS_ERR_INVALID; }
+    BuildState& S = *state_of(state);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Carver C{S.ws, S.o_scratch, S.ws_bytes};
+    auto* bits = C.take<uint32_t>((size_t)num_buckets * k);
+    auto* bucket_bits = C.take<unsigned long long>(num_buckets + 1);
+    if (!C.ok()) { set_error("workspace too small for %lld buckets of %d sub-streams", (long long)num_buckets, k); return MPS_ERR_WORKSPACE; }
+    if (num_buckets > 0) {
+        rect_walk_kernel<false><<<grid_for(num_buckets * k), 256, 0, st>>>(g, cb, nullptr, nullptr, bits, nullptr, S.d_flag);
+        rect_starts_kernel<<<grid_for(num_buckets, 64), 64, 0, st>>>(bits, bucket_row_offsets_i32, bucket_col_len_i32,
+                                                                     num_buckets, k, bucket_thread_startbit_u32, bucket_bits);
+    }
+    bucket_bases_kernel<<<1, 32, 0, st>>>(bucket_bits, num_buckets, reinterpret_cast<long long*>(bucket_bit_base_i64));
+    MPS_CUDA_TRY(cudaGetLastError());
+    long long total = 0; int flag = 0;
+    MPS_CUDA_TRY(cudaMemcpyAsync(&total, bucket_bit_base_i64 + num_buckets, sizeof(total), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaMemcpyAsync(&flag, S.d_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    if (flag == 3) { set_error("symbol not found and no ESC for (scale,ctx) key"); return (int)cudaErrorUnknown; }
+    *total_bits_out = total;
+    return MPS_OK;
+}
+
+int mps_build_rect_emit(mps_build_state* state, const uint16_t* bf16_bits, const uint8_t* ctx_bytes,
+                        const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
+                        const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
+                        const int32_t* row_indices_i32, int64_t num_buckets, int32_t k,
+                        const uint32_t* bucket_thread_startbit_u32, const int64_t* bucket_bit_base_i64,
+                        uint64_t* bitstream_u64, int64_t bitstream_words, void* stream) {
+    RectGeom g; CodeBook cb;
+    int rc = rect_common(state, bf16_bits, ctx_bytes, bucket_table_i32, bucket_col_start_i32, bucket_col_len_i32,
+                         bucket_row_offsets_i32, row_indices_i32, num_buckets, k, &g, &cb);
+    if (rc) return rc;
+    if (!bucket_thread_startbit_u32 || !bucket_bit_base_i64 || (bitstream_words > 0 && !bitstream_u64)) { set_error("sidecar emit: null argument"); return MPS_ERR_INVALID; }
+    BuildState& S = *state_of(state);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (bitstream_words > 0) MPS_CUDA_TRY(cudaMemsetAsync(bitstream_u64, 0, (size_t)bitstream_words * 8, st));
+    if (num_buckets > 0)
+        rect_walk_kernel<true><<<grid_for(num_buckets * k), 256, 0, st>>>(
+            g, cb, bucket_thread_startbit_u32, reinterpret_cast<const long long*>(bucket_bit_base_i64), nullptr,
+            reinterpret_cast<unsigned long long*>(bitstream_u64), S.d_flag);
+    MPS_CUDA_TRY(cudaGetLastError());
+    return MPS_OK;
+}
+
+}  // extern "C"

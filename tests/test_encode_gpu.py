@@ -1,0 +1,104 @@
+"""The GPU sidecar builder against the CPU oracle and the reference encoder's golden artifacts:
+every returned tensor byte-identical."""
+import numpy as np
+import pytest
+import torch
+
+from mpserve_b200 import workloads as wl
+from oracle import oracle as orc
+from tests._util import golden_names
+
+pytestmark = pytest.mark.gpu
+
+
+def _np(t):
+    return t.view(torch.uint16).numpy() if t.dtype == torch.bfloat16 else t.numpy()
+
+
+def _same(got: dict, want: dict, tag: str):
+    assert set(got) == set(want), (sorted(got), sorted(want))
+    for k, w in want.items():
+        g = _np(got[k].cpu())
+        assert g.dtype == w.dtype and g.shape == w.shape, (tag, k, g.dtype, w.dtype, g.shape, w.shape)
+        np.testing.assert_array_equal(g, w, err_msg=f"{tag}:{k}")
+
+
+@pytest.mark.parametrize("name", golden_names("fp8"))
+def test_fp8_builder_matches_reference_golden(golden_cases, name):
+    import MPServe_cuda
+
+    g = golden_cases[name]
+    p = g.params
+    got = MPServe_cuda.huffman_build_fp8_decode_tables(
+        torch.from_numpy(g.bf16).view(torch.bfloat16), torch.from_numpy(g.ctx), torch.from_numpy(g.scales),
+        max_len=p["max_len"], threads_per_block=p["threads_per_block"])
+    g.check_artifacts({k: _np(v) for k, v in got.items()})
+
+
+@pytest.mark.parametrize("name", [n for n in golden_names("awq") if n.endswith("_bucket")])
+def test_awq_bucket_builder_matches_reference_golden(golden_cases, name):
+    import MPServe_cuda
+
+    g = golden_cases[name]
+    p = g.params
+    got = MPServe_cuda.huffman_build_awq_int4_bucket_decode_tables(
+        torch.from_numpy(g.bf16).view(torch.bfloat16), torch.from_numpy(g.ctx), torch.from_numpy(g.scales),
+        max_len=p["max_len"], threads_per_block=p["threads_per_block"])
+    g.check_artifacts({k: _np(v) for k, v in got.items()})
+
+
+FP8_CASES = [
+    (512, 1024, "normal", "tensor", 7, 1024),
+    (300, 4096, "normal", "channel", 7, 1024),
+    (256, 512, "student_t", "block", 7, 256),
+    (1024, 1024, "student_t", "tensor", 7, 1024),
+    (129, 1000, "normal", "channel", 7, 1024),
+    (3, 5, "normal", "tensor", 7, 32),
+    (512, 512, "normal", "tensor", 5, 128),     # many ESC contexts at a short max_len
+    (512, 512, "normal", "tensor", 12, 256),
+    (2048, 2048, "student_t", "tensor", 7, 1024),
+]
+
+
+@pytest.mark.parametrize("case", FP8_CASES, ids=lambda c: "x".join(map(str, c)))
+def test_fp8_builder_matches_oracle(case):
+    import MPServe_cuda
+
+    n, m, dist, mode, L, k = case
+    c = wl.quantize_fp8(wl.random_weight(n, m, 300 + n + m, dist), mode)
+    want = orc.build_fp8(c.bf16.view(torch.uint16).numpy(), c.fp8_u8.numpy(), c.scales_u16.numpy(), L, k)
+    got = MPServe_cuda.huffman_build_fp8_decode_tables(c.bf16, c.fp8_u8, c.scales_u16, max_len=L, threads_per_block=k)
+    _same(got, want, str(case))
+
+
+@pytest.mark.parametrize("scale_kind,L", [("group", 11), ("row", 11), ("scalar", 11), ("scalar", 6), ("row", 8)])
+def test_awq_bucket_builder_matches_oracle(scale_kind, L):
+    import MPServe_cuda
+
+    n, m = 128, 512
+    c = wl.quantize_awq(wl.random_weight(n, m, 55, "student_t" if L != 11 else "normal"), 128)
+    sc = c.scales_u16
+    if scale_kind == "row":
+        sc = sc[:, 0].contiguous()
+    elif scale_kind == "scalar":
+        sc = sc[:1, 0].contiguous().reshape(1)
+    want = orc.build_awq_bucket(c.bf16.view(torch.uint16).numpy(), c.int4_u8.numpy(), sc.numpy(), L, 256)
+    got = MPServe_cuda.huffman_build_awq_int4_bucket_decode_tables(c.bf16, c.int4_u8, sc, max_len=L,
+                                                                   threads_per_block=256)
+    _same(got, want, f"{scale_kind} L={L}")
+
+
+def test_build_then_decode_roundtrip_on_device():
+    """Encoder output fed straight to the decoder, everything resident on the GPU."""
+    import MPServe_cuda
+    from mpserve_b200 import util
+
+    dev = torch.device("cuda:0")
+    n, m = 1024, 4096
+    c = wl.quantize_fp8(wl.random_weight(n, m, 9, "normal"), "channel")
+    art = MPServe_cuda.huffman_build_fp8_decode_tables(c.bf16.to(dev), c.fp8_u8.to(dev), c.scales_u16.to(dev),
+                                                       max_len=7, threads_per_block=1024)
+    assert art["bitstream_u64"].is_cuda
+    out = MPServe_cuda.huffman_decode_fp8(*util.decode_fp8_args(c.fp8_u8.to(dev), art, n, m, 7))
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu().view(torch.uint16), c.bf16.view(torch.uint16))
