@@ -481,7 +481,8 @@ using namespace mps;
 
 namespace {
 
-constexpr size_t kCubTempBytes = 96ull << 20;      // device-wide primitives' temporary storage
+// device-wide primitives' temporary storage: the radix sort may want a full extra key buffer
+static size_t cub_temp_bytes(int64_t numel) { return (64ull << 20) + (size_t)numel * 9; }
 constexpr size_t kCodebookScratch = 160ull << 20;  // interleaved per-context arrays of the codebook pass
 
 struct Carver {
@@ -509,7 +510,7 @@ extern "C" {
 size_t mps_build_workspace_bytes(int64_t numel, int64_t substreams) {
     if (numel < 0) numel = 0;
     if (substreams < numel) substreams = numel;
-    return 256 + (size_t)numel * 34 + (size_t)numel * 40 + (size_t)substreams * 4 + kCubTempBytes + kCodebookScratch +
+    return 256 + (size_t)numel * 34 + (size_t)numel * 40 + (size_t)substreams * 4 + cub_temp_bytes(numel) + kCodebookScratch +
            (1ull << 20);
 }
 
@@ -552,6 +553,7 @@ int mps_build_analyze(mps_build_state* state, const uint16_t* bf16_bits, const u
     auto* comp_a = C.take<unsigned long long>(numel);
     auto* comp_b = C.take<unsigned long long>(numel);
     auto* d_runs = C.take<long long>(4);
+    const size_t kCubTempBytes = cub_temp_bytes(numel);
     void* cub_tmp = C.take<uint8_t>(kCubTempBytes);
     if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
 
