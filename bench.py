@@ -36,6 +36,9 @@ from mpserve_b200 import workloads as wl  # noqa: E402
 METRIC = "decompressed_bf16_gbps"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one bucket_decode_kernel launch divided by its elements, from
+# the ncu capture summarised in profiles/ (a 218 M-element launch; traffic grows in proportion to the elements)
+NCU_TRAFFIC_BYTES_PER_ELEMENT = 3.757
 
 
 def log(*a):
@@ -370,7 +373,8 @@ def run_ours(args, rank, world, local_rank):
             "decode": f"one launch per step, threads={plan.threads}, chains={plan.chains}",
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": alg_bytes,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_ELEMENT * elements,
+                     "traffic_source": "ncu capture of a 218 M-element launch, scaled by elements", "peak_source": peak_src, "algorithmic_bytes_per_launch": alg_bytes,
                      "kernel_ms": kernel_ms_max},
         "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 16,
