@@ -176,7 +176,12 @@ MPS_API int mps_decode_bucket_batch(const mps_bucket_tensor* tensors_dev, const 
  *                the caller from the scale tensor: build_huffman.cu:611-696)
  *   rect_layout  fills bucket_thread_startbit [B,k+1] and bucket_bit_base [B+1], returns total bits
  *   rect_emit    fills bitstream_u64 [(total_bits+63)/64]
- * variant: 0 FP8 (context = fp8 byte), 1 AWQ-INT4 rectangular buckets (context = int4 code).
+ * variant: 0 FP8 (context = fp8 byte), 1 AWQ-INT4 rectangular buckets (context = int4 code),
+ *          2 AWQ-INT4 ragged buckets by exact scale (huffman_build_awq_int4_bucket_decode_tables_by_scale_entry,
+ *            kernel/build_huffman.cu:1074-1580; wrapper.cpp:290-321): pass bucket_col_len = NULL, the groups'
+ *            rows as row_indices, their column starts as bucket_col_start and the group offsets as
+ *            bucket_row_offsets to rect_layout / rect_emit; the group size is m for scalar / per-row scales,
+ *            sb1 for block scales.
  * scale_mode: 0 scalar, 1 per row [n], 2 two-dimensional blocks [n/sb0, nb1] of sb0 x sb1 elements. */
 typedef struct mps_build_state { unsigned char opaque[256]; } mps_build_state;
 

@@ -31,6 +31,7 @@ struct BuildState {
     int64_t N;                 // distinct (context, symbol) pairs
     int64_t G;                 // contexts
     int32_t L, variant;
+    int32_t group_size, pad_;  // elements per group of the ragged layout
     uint8_t* ws;               // device workspace base
     size_t ws_bytes;
     // offsets (bytes) into ws
@@ -179,7 +180,7 @@ __device__ bool package_merge_device(const CbScratch& S, int s, int n, int L) {
     return true;
 }
 
-// variant: V_FP8 or V_AWQ_BUCKET.  Tables are written at index g (contexts in ascending key order).
+// variant: V_FP8, V_AWQ_BUCKET or V_AWQ_BYSCALE.  Tables are written at index g (contexts in ascending key order).
 __global__ void codebook_kernel(const unsigned long long* __restrict__ items, const int* __restrict__ counts,
                                 const int* __restrict__ ctx_ofs, const int* __restrict__ perm, long long g0, long long g1,
                                 int L, int variant, CbScratch S, uint16_t* __restrict__ out_syms,
@@ -226,18 +227,45 @@ __global__ void codebook_kernel(const unsigned long long* __restrict__ items, co
             if (c == fb) ++seen;
             const uint32_t sy = (uint32_t)(items[j] & 0xFFFF);
             if (!kept) { esc_w += c; enc[j] = 0; }
-            if (!cand_done) {
-                if (kept && sy == cand) ++cand;
+            if (!cand_done) {  // smallest symbol not among the kept ones (by-scale: not in the context at all)
+                if ((kept || variant == V_AWQ_BYSCALE) && sy == cand) ++cand;
                 else if (sy > cand) cand_done = true;
             }
         }
         esc_sym = (uint16_t)(cand <= 0xFFFFu ? cand : 0xFFFFu);
         int esc_i = (int)esc_w;                        // the reference accumulates in int
-        if (variant != V_FP8 && esc_i <= 0) esc_i = 1;
-        // final list, ascending by (weight, symbol): perm[lo, lo+r), perm[hi, b), ESC inserted in order
+        if (variant == V_AWQ_BUCKET && esc_i <= 0) esc_i = 1;
         n = 0;
         bool placed = false;
-        for (int q = 0; q < keepk; ++q) {
+        if (variant == V_AWQ_BYSCALE) {
+            // The by-scale builder keeps the kept items in DESCENDING order with the ESC item last and
+            // does not re-sort them (build_huffman.cu:1283-1301), while the lengths it pairs them with
+            // positionally are those of the ASCENDING weights: weights go in ascending, symbols in
+            // descending order (classes from the most frequent down, ascending symbol inside a class).
+            int wq = 0;  // ascending weights with the ESC weight merged in
+            for (int q = 0; q < keepk; ++q) {
+                const int j = perm[q < r ? lo + q : hi + (q - r)];
+                const unsigned long long w = (unsigned long long)(uint32_t)counts[j];
+                if (!placed && (unsigned long long)(uint32_t)esc_i <= w) { AT(S.w, wq) = (unsigned long long)(uint32_t)esc_i; ++wq; placed = true; }
+                AT(S.w, wq) = w; ++wq;
+            }
+            if (!placed) { AT(S.w, wq) = (unsigned long long)(uint32_t)esc_i; ++wq; }
+            int top = b;  // classes are runs of equal count in perm[a, b)
+            while (n < keepk) {
+                int cs = top - 1;
+                const int f = counts[perm[cs]];
+                while (cs > a && counts[perm[cs - 1]] == f) --cs;
+                for (int q = cs; q < top && n < keepk; ++q) {
+                    const int j = perm[q];
+                    AT(S.sym, n) = (uint16_t)(items[j] & 0xFFFF); AT(S.src, n) = j; ++n;
+                }
+                top = cs;
+            }
+            AT(S.sym, n) = esc_sym; AT(S.src, n) = -1; esc_pos = n; ++n;
+            placed = true;
+        }
+        // final list, ascending by (weight, symbol): perm[lo, lo+r), perm[hi, b), ESC inserted in order
+        for (int q = 0; q < keepk && variant != V_AWQ_BYSCALE; ++q) {
             const int j = perm[q < r ? lo + q : hi + (q - r)];
             const unsigned long long w = (unsigned long long)(uint32_t)counts[j];
             const uint16_t sy = (uint16_t)(items[j] & 0xFFFF);
@@ -257,7 +285,7 @@ __global__ void codebook_kernel(const unsigned long long* __restrict__ items, co
         }
     }
     if (!package_merge_device(S, s, n, L)) { atomicExch(err, 2); return; }
-    if (use_esc && variant == V_AWQ_BUCKET) AT(S.len, esc_pos) = (uint8_t)L;  // ESC code forced to L bits (:1812-1816)
+    if (use_esc && variant != V_FP8) AT(S.len, esc_pos) = (uint8_t)L;  // ESC code forced to L bits (:1812-1816)
 
     // canonical codes handed out in item order within each length (build_huffman.cu:171-203)
     uint32_t next_code[17];
@@ -283,7 +311,7 @@ __global__ void codebook_kernel(const unsigned long long* __restrict__ items, co
             if (idx < (uint32_t)TS) { tsym[idx] = sy; set_nibble(tlen, idx, nib); }
         }
     }
-    if (use_esc && variant == V_AWQ_BUCKET) {  // every slot that shows the ESC symbol is marked 15 (:1822-1829)
+    if (use_esc && variant != V_FP8) {  // every slot that shows the ESC symbol is marked 15 (:1822-1829)
         for (int i = 0; i < TS; ++i)
             if (tsym[i] == esc_sym) set_nibble(tlen, i, 15u);
     }
@@ -344,8 +372,9 @@ struct RectGeom {
     const int32_t* col_len;           // [B]
     const int32_t* row_ofs;           // [B+1]
     const int32_t* rows;              // row lists
+    const int32_t* group_col;         // ragged buckets: column start of every listed group, else nullptr
     long long B, m;
-    int k, nctx;
+    int k, nctx, group_size;          // group_size: elements per group (ragged buckets)
     uint32_t ctx_mask;
 };
 
@@ -391,7 +420,8 @@ __global__ void rect_walk_kernel(RectGeom g, CodeBook cb, const uint32_t* __rest
         const int t = (int)(id - b * g.k);
         const int row_a = g.row_ofs[b];
         const long long nrows = g.row_ofs[b + 1] - row_a;
-        const long long col_len = g.col_len[b], col_start = g.col_start[b];
+        const long long col_len = g.group_col ? g.group_size : g.col_len[b];
+        const long long col_start = g.group_col ? 0 : g.col_start[b];
         const long long total = nrows * col_len;
         long long k_eff = total < 1 ? 1 : total;
         if (k_eff > g.k) k_eff = g.k;
@@ -406,7 +436,7 @@ __global__ void rect_walk_kernel(RectGeom g, CodeBook cb, const uint32_t* __rest
         unsigned long long bits = 0;
         long long rr = t / col_len, cc = t - rr * col_len;
         for (long long e = t; e < total; e += k_eff) {
-            const long long i = (long long)g.rows[row_a + rr] * g.m + col_start + cc;
+            const long long i = (long long)g.rows[row_a + rr] * g.m + (g.group_col ? g.group_col[row_a + rr] : col_start) + cc;
             const int gid = bt[g.ctx[i] & g.ctx_mask];
             uint32_t code = 0; int len = 0; bool raw = false;
             const uint32_t sym = g.sym[i];
@@ -436,10 +466,10 @@ __global__ void rect_walk_kernel(RectGeom g, CodeBook cb, const uint32_t* __rest
 
 // per bucket: start bit of every sub-stream relative to the bucket (build_huffman.cu:869-879)
 __global__ void rect_starts_kernel(const uint32_t* __restrict__ bits, const int32_t* __restrict__ row_ofs,
-                                   const int32_t* __restrict__ col_len, long long B, int k, uint32_t* __restrict__ startbit,
-                                   unsigned long long* __restrict__ bucket_bits) {
+                                   const int32_t* __restrict__ col_len, int group_size, long long B, int k,
+                                   uint32_t* __restrict__ startbit, unsigned long long* __restrict__ bucket_bits) {
     for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < B; b += (long long)gridDim.x * blockDim.x) {
-        const long long total = (long long)(row_ofs[b + 1] - row_ofs[b]) * col_len[b];
+        const long long total = (long long)(row_ofs[b + 1] - row_ofs[b]) * (col_len ? col_len[b] : group_size);
         long long k_eff = total < 1 ? 1 : total;
         if (k_eff > k) k_eff = k;
         uint32_t* st = startbit + b * ((long long)k + 1);
@@ -523,7 +553,7 @@ int mps_build_analyze(mps_build_state* state, const uint16_t* bf16_bits, const u
         return MPS_ERR_INVALID;
     }
     if (n <= 0 || m <= 0) { set_error("bf16_params shape must be non-empty"); return MPS_ERR_INVALID; }
-    if (variant != V_FP8 && variant != V_AWQ_BUCKET) { set_error("this builder variant is not implemented on the GPU yet"); return MPS_ERR_UNSUPPORTED; }
+    if (variant != V_FP8 && variant != V_AWQ_BUCKET && variant != V_AWQ_BYSCALE) { set_error("this builder variant is not implemented on the GPU yet"); return MPS_ERR_UNSUPPORTED; }
     if (max_len <= 0 || max_len > 15) { set_error("max_len must be in [1, 15]"); return MPS_ERR_INVALID; }
     if (scale_mode < 0 || scale_mode > 2 || (scale_mode == 2 && (nb1 <= 0 || sb0 <= 0 || sb1 <= 0))) {
         set_error("unsupported scales layout");
@@ -536,6 +566,7 @@ int mps_build_analyze(mps_build_state* state, const uint16_t* bf16_bits, const u
     BuildState& S = *state_of(state);
     memset(&S, 0, sizeof(S));
     S.numel = numel; S.n = n; S.m = m; S.L = (int32_t)max_len; S.variant = variant;
+    S.group_size = (int32_t)((scale_mode == 2) ? sb1 : m);
     S.ws = static_cast<uint8_t*>(workspace); S.ws_bytes = workspace_bytes;
     Carver C{S.ws, 256, workspace_bytes};
     S.d_flag = reinterpret_cast<int32_t*>(S.ws);
@@ -688,13 +719,19 @@ static int rect_common(mps_build_state* state, const uint16_t* bf16_bits, const 
                        const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,
                        const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
                        const int32_t* row_indices_i32, int64_t num_buckets, int32_t k, RectGeom* g, CodeBook* cb) {
-    if (!state || !bf16_bits || !ctx_bytes || !bucket_table_i32 || !bucket_col_start_i32 || !bucket_col_len_i32 ||
+    if (!state || !bf16_bits || !ctx_bytes || !bucket_table_i32 || !bucket_col_start_i32 ||
         !bucket_row_offsets_i32 || !row_indices_i32 || num_buckets < 0 || k <= 0 || k > 1024) {
         set_error("sidecar layout: bad argument");
         return MPS_ERR_INVALID;
     }
     BuildState& S = *state_of(state);
-    g->sym = bf16_bits; g->ctx = ctx_bytes; g->bucket_table = bucket_table_i32; g->col_start = bucket_col_start_i32;
+    // ragged (by-scale) layout: bucket_col_len is null, bucket_col_start lists the column start of every
+    // group, the row list holds the groups' rows and every group has S.group_size elements
+    const bool ragged = (bucket_col_len_i32 == nullptr);
+    if (ragged && S.group_size <= 0) { set_error("sidecar layout: group size not set"); return MPS_ERR_INVALID; }
+    g->sym = bf16_bits; g->ctx = ctx_bytes; g->bucket_table = bucket_table_i32;
+    g->col_start = ragged ? nullptr : bucket_col_start_i32; g->group_col = ragged ? bucket_col_start_i32 : nullptr;
+    g->group_size = S.group_size;
     g->col_len = bucket_col_len_i32; g->row_ofs = bucket_row_offsets_i32; g->rows = row_indices_i32;
     g->B = num_buckets; g->m = S.m; g->k = k; g->nctx = (S.variant == V_FP8) ? 256 : 16;
     g->ctx_mask = (S.variant == V_FP8) ? 0xFFu : 0x0Fu;
@@ -725,8 +762,8 @@ int mps_build_rect_layout(mps_build_state* state, const uint16_t* bf16_bits, con
     if (!C.ok()) { set_error("workspace too small for %lld buckets of %d sub-streams", (long long)num_buckets, k); return MPS_ERR_WORKSPACE; }
     if (num_buckets > 0) {
         rect_walk_kernel<false><<<grid_for(num_buckets * k), 256, 0, st>>>(g, cb, nullptr, nullptr, bits, nullptr, S.d_flag);
-        rect_starts_kernel<<<grid_for(num_buckets, 64), 64, 0, st>>>(bits, bucket_row_offsets_i32, bucket_col_len_i32,
-                                                                     num_buckets, k, bucket_thread_startbit_u32, bucket_bits);
+        rect_starts_kernel<<<grid_for(num_buckets, 64), 64, 0, st>>>(bits, bucket_row_offsets_i32, g.group_col ? nullptr : bucket_col_len_i32,
+                                                                     g.group_size, num_buckets, k, bucket_thread_startbit_u32, bucket_bits);
     }
     bucket_bases_kernel<<<1, 32, 0, st>>>(bucket_bits, num_buckets, reinterpret_cast<long long*>(bucket_bit_base_i64));
     MPS_CUDA_TRY(cudaGetLastError());

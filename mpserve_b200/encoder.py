@@ -205,8 +205,112 @@ def build_awq_bucket(bf16_params, int4_values_u8, scales_u16, max_len, threads_p
                        "int4_values_u8")
 
 
+def ragged_buckets(scales_u16: np.ndarray, mode: int, n: int, m: int, nb1: int, sb0: int, sb1: int, group_cap: int):
+    """Groups (row, col_start) sorted by (scale, row, col) and cut into buckets of <= group_cap groups of
+    one scale (build_huffman.cu:1353-1392)."""
+    s = scales_u16.reshape(-1)
+    if mode == 2:
+        gpr, gsize = nb1, sb1
+        rows = np.repeat(np.arange(n, dtype=np.int64), gpr)
+        bcs = np.tile(np.arange(gpr, dtype=np.int64), n)
+        sc = s.reshape(-1, nb1)[rows // sb0, bcs]
+        c0 = bcs * sb1
+    else:
+        gpr, gsize = 1, m
+        rows = np.arange(n, dtype=np.int64)
+        c0 = np.zeros(n, dtype=np.int64)
+        sc = np.full(n, s[0], dtype=np.uint16) if mode == 0 else s.astype(np.uint16)
+    order = np.lexsort((c0, rows, sc))
+    sc, rows, c0 = sc[order], rows[order], c0[order]
+    starts = np.flatnonzero(np.r_[True, sc[1:] != sc[:-1]])
+    ends = np.r_[starts[1:], sc.size]
+    b_scale, b_ofs = [], [0]
+    for a, e in zip(starts, ends):
+        for off in range(a, e, group_cap):
+            b_scale.append(sc[a])
+            b_ofs.append(min(off + group_cap, e))
+    return (np.asarray(b_scale, dtype=np.uint16), np.asarray(b_ofs, dtype=np.int32), rows.astype(np.int32),
+            c0.astype(np.int32), int(gsize))
+
+
 def build_awq_by_scale(bf16_values, int4_values, scales_u16, max_len, threads, group_cap):
-    _missing("huffman_build_awq_int4_bucket_decode_tables_by_scale")
+    """huffman_build_awq_int4_bucket_decode_tables_by_scale (wrapper.cpp:290-321, build_huffman.cu:1074-1580)."""
+    for t in (bf16_values, int4_values, scales_u16):
+        if not isinstance(t, torch.Tensor):
+            raise ValueError("inputs must be defined")
+    if bf16_values.dtype != torch.bfloat16:
+        raise ValueError("bf16_params must be torch.bfloat16")
+    if int4_values.dtype != torch.uint8:
+        raise ValueError("int4_values_u8 must be torch.uint8")
+    if scales_u16.dtype != torch.uint16:
+        raise ValueError("scales_u16 must be torch.uint16 (bf16 raw bits)")
+    if max_len <= 0 or max_len > 15:
+        raise ValueError("max_len must be in (0,15]")
+    if threads <= 0 or threads > 1024:
+        raise ValueError("threads_per_block must be in [1,1024]")
+    if group_cap <= 0:
+        raise ValueError("group_cap must be > 0")
+    if bf16_values.dim() != 2:
+        raise ValueError("bf16_params must be 2D [n,m]")
+    if tuple(int4_values.shape) != tuple(bf16_values.shape):
+        raise ValueError("int4_values_u8 shape must match bf16_params")
+    lib = _lib.load()
+    dev = _device()
+    n, m = int(bf16_values.size(0)), int(bf16_values.size(1))
+    if n <= 0 or m <= 0:
+        raise ValueError("bf16_params shape must be non-empty")
+    s16 = scales_u16.contiguous()
+    mode, nb0, nb1, sb0, sb1 = _scale_mode(s16, n, m, False)
+    L, k = int(max_len), int(threads)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        sym_d = bf16_values.contiguous().view(torch.uint16).to(dev)
+        ctx_d = int4_values.contiguous().to(dev)
+        sc_d = s16.to(dev)
+        b_scale, b_ofs, g_rows, g_cols, gsize = ragged_buckets(s16.cpu().numpy(), mode, n, m, nb1, sb0, sb1,
+                                                               int(group_cap))
+        B = int(b_scale.size)
+        ws_bytes = int(lib.mps_build_workspace_bytes(n * m, max(n * m, B * k)))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        state = (C.c_ubyte * 256)()
+        G, N = C.c_int64(0), C.c_int64(0)
+        _lib.check(lib.mps_build_analyze(state, sym_d.data_ptr(), ctx_d.data_ptr(), sc_d.data_ptr(), mode, nb1, sb0, sb1,
+                                         n, m, 2, L, ws.data_ptr(), ws_bytes, stream, C.byref(G), C.byref(N)))
+        G = int(G.value)
+        TS = 1 << L
+        syms = torch.empty((G, TS), dtype=torch.uint16, device=dev)
+        lens = torch.empty((G, TS // 2), dtype=torch.uint8, device=dev)
+        tscale = torch.empty((G,), dtype=torch.uint16, device=dev)
+        tctx = torch.empty((G,), dtype=torch.uint16, device=dev)
+        _lib.check(lib.mps_build_codebooks(state, syms.data_ptr(), lens.data_ptr(), tscale.data_ptr(), tctx.data_ptr(),
+                                           stream))
+        b_scale_d = torch.from_numpy(b_scale).to(dev)
+        b_ofs_d = torch.from_numpy(b_ofs).to(dev)
+        rows_d = torch.from_numpy(g_rows).to(dev)
+        cols_d = torch.from_numpy(g_cols).to(dev)
+        btab = torch.empty((B, 16), dtype=torch.int32, device=dev)
+        _lib.check(lib.mps_build_bucket_table(state, b_scale_d.data_ptr(), B, btab.data_ptr(), stream))
+        tsb = torch.empty((B, k + 1), dtype=torch.uint32, device=dev)
+        bbase = torch.empty((B + 1,), dtype=torch.int64, device=dev)
+        total = C.c_int64(0)
+        _lib.check(lib.mps_build_rect_layout(state, sym_d.data_ptr(), ctx_d.data_ptr(), btab.data_ptr(),
+                                             cols_d.data_ptr(), None, b_ofs_d.data_ptr(), rows_d.data_ptr(), B, k,
+                                             tsb.data_ptr(), bbase.data_ptr(), stream, C.byref(total)))
+        words = (int(total.value) + 63) >> 6
+        bits = torch.empty((words,), dtype=torch.uint64, device=dev)
+        _lib.check(lib.mps_build_rect_emit(state, sym_d.data_ptr(), ctx_d.data_ptr(), btab.data_ptr(), cols_d.data_ptr(),
+                                           None, b_ofs_d.data_ptr(), rows_d.data_ptr(), B, k, tsb.data_ptr(),
+                                           bbase.data_ptr(), bits.data_ptr(), words, stream))
+        out = {
+            "decode_syms_u16": syms, "decode_lens_u8": lens, "table_scale_u16": tscale, "table_qv_u16": tctx,
+            "bucket_scale_u16": b_scale_d, "bucket_group_offsets_i32": b_ofs_d, "group_rows_i32": rows_d,
+            "group_col_start_i32": cols_d, "bucket_table_i32": btab, "bucket_thread_startbit_u32": tsb,
+            "bucket_bit_base_i64": bbase, "bitstream_u64": bits,
+            "shape_nmkg_i64": torch.tensor([n, m, k, gsize], dtype=torch.int64),
+        }
+        torch.cuda.synchronize(dev)
+        keep_on_device = bf16_values.is_cuda
+        return {k_: (v if keep_on_device and v.is_cuda else v.cpu()) for k_, v in out.items()}
 
 
 def build_awq_shared(bf16_params, int4_values_u8, scales_u16, max_len):

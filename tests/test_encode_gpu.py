@@ -88,6 +88,36 @@ def test_awq_bucket_builder_matches_oracle(scale_kind, L):
     _same(got, want, f"{scale_kind} L={L}")
 
 
+@pytest.mark.parametrize("name", [n for n in golden_names("awq") if n.endswith("_byscale")])
+def test_awq_by_scale_builder_matches_reference_golden(golden_cases, name):
+    import MPServe_cuda
+
+    g = golden_cases[name]
+    p = g.params
+    got = MPServe_cuda.huffman_build_awq_int4_bucket_decode_tables_by_scale(
+        torch.from_numpy(g.bf16).view(torch.bfloat16), torch.from_numpy(g.ctx), torch.from_numpy(g.scales),
+        max_len=p["max_len"], threads=p["threads"], group_cap=p["group_cap"])
+    g.check_artifacts({k: _np(v) for k, v in got.items()})
+
+
+@pytest.mark.parametrize("scale_kind,L,cap", [("group", 11, 1024), ("row", 11, 5), ("scalar", 11, 1024),
+                                                 ("scalar", 6, 3), ("row", 8, 1024)])
+def test_awq_by_scale_builder_matches_oracle(scale_kind, L, cap):
+    import MPServe_cuda
+
+    n, m = 128, 512
+    c = wl.quantize_awq(wl.random_weight(n, m, 56, "student_t" if L != 11 else "normal"), 128)
+    sc = c.scales_u16
+    if scale_kind == "row":
+        sc = sc[:, 0].contiguous()
+    elif scale_kind == "scalar":
+        sc = sc[:1, 0].contiguous().reshape(1)
+    want = orc.build_awq_by_scale(c.bf16.view(torch.uint16).numpy(), c.int4_u8.numpy(), sc.numpy(), L, 256, cap)
+    got = MPServe_cuda.huffman_build_awq_int4_bucket_decode_tables_by_scale(c.bf16, c.int4_u8, sc, max_len=L,
+                                                                            threads=256, group_cap=cap)
+    _same(got, want, f"{scale_kind} L={L}")
+
+
 def test_build_then_decode_roundtrip_on_device():
     """Encoder output fed straight to the decoder, everything resident on the GPU."""
     import MPServe_cuda
