@@ -74,7 +74,13 @@ struct BatchArgs {
 #ifndef MPS_STAGES
 #define MPS_STAGES 3
 #endif
-constexpr int kStages = MPS_STAGES;            // context-byte ring: stages of kSteps steps each
+constexpr int kStages = MPS_STAGES;            // context-byte ring: stages of kSS steps each for the widest items
+constexpr int kMaxStages = 4 * kStages;        // narrower items split the same ring into more stages
+// Stages of the context ring for items of `span` sub-streams: a narrow item leaves each decoding
+// thread waiting on memory latency rather than on issue slots, so it needs more steps in flight.
+__host__ __device__ constexpr uint32_t ring_stages(uint32_t span) {
+    return (kStages * 1024u / span) < (uint32_t)kMaxStages ? (kStages * 1024u / span) : (uint32_t)kMaxStages;
+}
 constexpr int kMaxSpan = 1024;        // sub-streams per work item (threads x chains), at most
 
 // ------------------------------------------------------------------------------------------------
@@ -111,8 +117,8 @@ struct Smem {
                                                  // one set for the item being decoded, one being prepared
     Prepared prep[2];
     long long prefix[kPrefixCap + 1];
-    unsigned long long full_bar[kStages];        // bulk copies of a stage have landed
-    unsigned long long empty_bar[kStages];       // every warp is done reading a stage
+    unsigned long long full_bar[kMaxStages];     // bulk copies of a stage have landed
+    unsigned long long empty_bar[kMaxStages];    // every warp is done reading a stage
     int32_t gid[256];                            // context -> table id of the staged tables
     int32_t gid_next[256];                       // same for the prepared item (written by the scout once the
                                                  // decoding warps have taken the previous contents)
@@ -343,7 +349,7 @@ __device__ __forceinline__ void decode_vec(const Smem& sm, const uint32_t* rowba
 // into shared memory, deep enough ahead of use to cover HBM latency at full rate (Little's law
 // wants tens of KB in flight per SM; register prefetch gave a few KB).
 //
-//  * Context bytes: one elected thread issues cp.async.bulk (the TMA bulk-copy engine, no tensor
+//  * Context bytes: a dedicated producer warp issues cp.async.bulk (the TMA bulk-copy engine, no tensor
 //    map, no multicast) of the SPAN contiguous bytes every step needs, kSteps steps per stage,
 //    kStages stages ahead; stages are handed over with full/empty mbarriers.  Consumers read their
 //    CH bytes of a step with one conflict-free shared-memory load.
@@ -412,9 +418,12 @@ __device__ __forceinline__ void lds_ordered_if(uint32_t& v, uint32_t addr, uint3
 struct BitOrigin {        // bitstream of the item seen from a 16-byte aligned origin
     const uint8_t* base;  // 16-byte aligned
     uint32_t last_ofs;    // largest 16-byte aligned offset whose chunk lies wholly inside the bitstream
+    uint32_t tail_ofs;    // offset of a final 8-byte half chunk (bitstream ends mid-chunk), else 0xFFFFFFFF
     uint32_t bit_delta;   // bits between the origin and the bucket's first bit (0 or 64)
 };
 
+constexpr int kMaxGrab = 8;          // most work items one CTA takes from the queue at once
+constexpr int kGrabSlack = 4;        // a grab is at most 1/(kGrabSlack * CTAs) of what is left
 constexpr int kRingChunks = 4;                        // 16-byte chunks of bitstream kept per sub-stream
 constexpr uint32_t kRingBytes = 16u * kRingChunks;    // 64
 
@@ -450,13 +459,28 @@ __device__ __forceinline__ uint32_t schain_window(SChain& ch, uint32_t ring, uin
 __device__ __forceinline__ void schain_request(SChain& ch, uint32_t ring, const BitOrigin& bo) {
     const uint32_t need = (((ch.pos >> 5) + 1) >> 2) + kRingChunks;  // chunks below `need` must be on their way
     const uint32_t ofs = ch.next << 4;
-    const uint8_t* src = bo.base + min(ofs, bo.last_ofs);           // clamped: never outside the bitstream
+    const uint8_t* src = bo.base + ofs;
     const uint32_t dst = ring + (ofs & (kRingBytes - 1));
+    // a chunk past the end of the bitstream is never copied (its ring slot keeps stale bits that no
+    // valid sub-stream decodes from); a bitstream that ends mid-chunk gives up its last 8 bytes alone
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %0, %1;\n\t@p cp.async.cg.shared.global [%2], [%3], 16;\n\t@p add.u32 %0, %0, 1;\n\t}"
+        "{\n\t.reg .pred p, q, r;\n\t"
+        "setp.lt.u32 p, %0, %1;\n\t"
+        "setp.le.and.u32 q, %4, %5, p;\n\t"
+        "setp.eq.and.u32 r, %4, %6, p;\n\t"
+        "@q cp.async.cg.shared.global [%2], [%3], 16;\n\t"
+        "@r cp.async.ca.shared.global [%2], [%3], 8;\n\t"
+        "@p add.u32 %0, %0, 1;\n\t}"
         : "+r"(ch.next)
-        : "r"(need), "r"(dst), "l"(src)
+        : "r"(need), "r"(dst), "l"(src), "r"(ofs), "r"(bo.last_ofs), "r"(bo.tail_ofs)
         : "memory");
+}
+
+// First chunks of a sub-stream (same rules as schain_request, plain control flow).
+__device__ __forceinline__ void chunk_fetch(uint32_t ring, const BitOrigin& bo, uint32_t ofs) {
+    const uint32_t dst = ring + (ofs & (kRingBytes - 1));
+    if (ofs <= bo.last_ofs) cp_async_16(dst, bo.base + ofs);
+    else if (ofs == bo.tail_ofs) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(bo.base + ofs) : "memory");
 }
 
 template <int CH>
@@ -484,34 +508,36 @@ struct StreamItem {
     uint32_t t_begin, k_eff, col_len, nsteps;
 };
 
-// Copies of block `jb` of the item (producer lane only).  Returns false if the stage never freed.
+// Producer warp.  Lane 0 waits until every consumer warp has released the stage and arms its "full"
+// barrier with the bytes to come; lanes 0..kSS-1 then issue one bulk copy each (the context bytes of
+// one step), so a block of steps costs the producer one round of address arithmetic, not kSS rounds
+// back to back.  The producer never decodes, so consumers are never held back by a slow sibling: they
+// only ever wait for data.  Returns false if a stage never freed.
 template <int SPAN>
-__device__ __forceinline__ bool producer_issue(Smem& sm, const StreamItem& it, uint32_t g, uint32_t jb, uint32_t& p_rr,
-                                               uint32_t& p_cc) {
-    const uint32_t stage = g % kStages, round = g / kStages;
-    const uint32_t full = smem_u32(&sm.full_bar[stage]);
-    if (!mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u)) return false;
-    const uint32_t left = it.nsteps - jb * kSS;
-    const uint32_t nst = left < (uint32_t)kSS ? left : (uint32_t)kSS;
-    mbar_expect_tx(full, nst * SPAN);
-    for (uint32_t u = 0; u < nst; ++u) {
-        const uint8_t* src = it.ctx_bytes + it.rowbase[p_rr < kRowCap ? p_rr : 0] + p_cc + it.t_begin;
-        bulk_g2s(smem_u32(sm.ctxring) + (stage * kSS + u) * SPAN, src, SPAN, full);
-        p_cc += it.k_eff;
-        if (p_cc >= it.col_len) { p_cc = 0; ++p_rr; }
+__device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uint32_t blk, uint32_t nblocks) {
+    constexpr uint32_t NST = ring_stages(SPAN);
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t spr = it.col_len / it.k_eff;  // steps per row of the bucket (col_len is a multiple of k_eff here)
+    for (uint32_t jb = 0; jb < nblocks; ++jb) {
+        const uint32_t g = blk + jb, stage = g % NST, round = g / NST;
+        const uint32_t full = smem_u32(&sm.full_bar[stage]);
+        const uint32_t left = it.nsteps - jb * kSS;
+        const uint32_t nst = left < (uint32_t)kSS ? left : (uint32_t)kSS;
+        int good = 1;
+        if (lane == 0) {
+            good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u) ? 1 : 0;
+            if (good) mbar_expect_tx(full, nst * SPAN);
+        }
+        good = __shfl_sync(0xFFFFFFFFu, good, 0);
+        if (!good) return false;
+        if (lane < nst) {
+            const uint32_t s = jb * kSS + lane;
+            const uint32_t rr = s / spr, cc = (s - rr * spr) * it.k_eff;
+            const uint8_t* src = it.ctx_bytes + it.rowbase[rr < kRowCap ? rr : 0] + cc + it.t_begin;
+            bulk_g2s(smem_u32(sm.ctxring) + (stage * kSS + lane) * SPAN, src, SPAN, full);
+        }
     }
     return true;
-}
-
-// Producer side (one lane of the dedicated producer warp).  `upto` blocks are issued, each after its
-// stage was released by every consumer warp.  The producer never decodes, so consumers are never
-// held back by a slow sibling: they only ever wait for data.
-template <int SPAN>
-__device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uint32_t blk, uint32_t& p_next,
-                                             uint32_t& p_rr, uint32_t& p_cc, uint32_t upto) {
-    bool ok = true;
-    for (; p_next < upto && ok; ++p_next) ok = producer_issue<SPAN>(sm, it, blk + p_next, p_next, p_rr, p_cc);
-    return ok;
 }
 
 template <int L, int THREADS, int CH>
@@ -533,7 +559,7 @@ __device__ __forceinline__ void stream_begin(Smem& sm, const StreamItem& it, Str
 #pragma unroll
         for (int q = 0; q < kRingChunks; ++q) {
             const uint32_t ofs = (c0 + q) << 4;
-            cp_async_16(ring + (ofs & (kRingBytes - 1)), it.bo.base + min(ofs, it.bo.last_ofs));
+            chunk_fetch(ring, it.bo, ofs);
         }
         st.ch[c].next = c0 + kRingChunks;
     }
@@ -544,7 +570,10 @@ template <int L, int THREADS, int CH, bool ESC>
 __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st,
                                            uint32_t blk) {
     constexpr int RP = ESC ? 1 : ((32 - L) / L + 1);   // symbols per 32-bit window
-    constexpr int CHK = ESC ? 4 : ((2 * kSS * L < 128) ? 2 * kSS : kSS);  // steps between bitstream requests
+    // Steps between bitstream requests: rare requests cost fewer instructions, frequent ones let
+    // cp.async.wait_group leave more of them in flight, which is what a thread with few chains needs.
+    constexpr int CHK_MAX = (2 * kSS * L < 128) ? 2 * kSS : kSS;
+    constexpr int CHK = ESC ? 4 : (4 * CH < CHK_MAX ? 4 * CH : CHK_MAX);
     constexpr int MAXBITS = ESC ? (L + 16) : L;          // most bits one step can consume
     static_assert(CHK * MAXBITS < 128, "at most one chunk boundary between two requests");
     // A chunk requested when w1 enters chunk k is first read when w1 enters chunk k + kRingChunks - 1,
@@ -553,6 +582,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
     constexpr int NEED = ((kRingChunks - 1) * 128 + MAXBITS - 1) / MAXBITS;
     constexpr int LAG = (NEED / CHK - 2) > 0 ? (NEED / CHK - 2) : 0;
     constexpr uint32_t SPAN = THREADS * CH;
+    constexpr uint32_t NST = ring_stages(SPAN);
     static_assert(kSS % RP == 0 && (kSS % CHK == 0 || CHK == 2 * kSS), "a stage must hold whole windows and request periods");
     using CT = typename Ctx<CH>::T;
     const uint32_t tid = threadIdx.x;
@@ -579,7 +609,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
     const uint32_t nblocks = (it.nsteps + kSS - 1) / kSS;
 
     for (uint32_t jb = 0; jb < nblocks; ++jb) {
-        const uint32_t g = blk + jb, stage = g % kStages, round = g / kStages;
+        const uint32_t g = blk + jb, stage = g % NST, round = g / NST;
         if (!mbar_wait(smem_u32(&sm.full_bar[stage]), round & 1u)) return false;
         const uint32_t left = it.nsteps - jb * kSS;
         const uint32_t count = left < (uint32_t)kSS ? left : (uint32_t)kSS;
@@ -774,15 +804,31 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
 
 template <int L, int THREADS, int CH>
 __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws, int slot, bool prefix_cached,
-                              int wait_iter) {
+                              int wait_iter, int& q_cur, int& q_end) {
     constexpr int NCTX = (L == 7) ? 256 : 16;
     constexpr int TS = 1 << L;
     constexpr uint32_t SPAN = THREADS * CH;
     const int lane = threadIdx.x & 31;
     Prepared& P = sm.prep[slot];
-    int item = 0;
-    if (lane == 0) item = (int)atomicAdd(&ws[0], 1u);
-    item = __shfl_sync(0xFFFFFFFFu, item, 0);
+    // Work queue with guided grabs: consecutive items belong to the same tensor more often than not, so
+    // a CTA that takes several in a row stages that tensor's tables once for all of them.  The grab
+    // shrinks to single items towards the end of the launch, where balance matters more than reuse.
+    if (q_cur >= q_end) {
+        const int remaining = args.total_items - q_cur;  // q_cur: end of this CTA's last grab, a lower bound of the queue head
+        int want = remaining / (int)(kGrabSlack * gridDim.x);
+        want = want < 1 ? 1 : (want > kMaxGrab ? kMaxGrab : want);
+        unsigned int start = 0;
+        if (lane == 0) start = atomicAdd(&ws[0], (unsigned int)want);
+        start = __shfl_sync(0xFFFFFFFFu, start, 0);
+        if (start >= (unsigned int)args.total_items) {
+            q_cur = q_end = args.total_items;  // queue exhausted
+        } else {
+            q_cur = (int)start;
+            q_end = (args.total_items - q_cur < want) ? args.total_items : q_cur + want;
+        }
+    }
+    const int item = q_cur;
+    if (item < args.total_items) ++q_cur;
     if (item >= args.total_items) {
         if (lane == 0) P.valid = 0;
         __syncwarp();
@@ -892,7 +938,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
     constexpr int NT = THREADS + 64;         // decoding threads + producer warp + scout warp
     const int tid = threadIdx.x;
     const bool is_consumer = tid < THREADS;
-    const bool is_producer = tid == THREADS;        // first lane of the producer warp
+    const bool is_producer = tid >= THREADS && tid < THREADS + 32;  // the whole producer warp
     const bool is_scout = tid >= THREADS + 32;       // the whole scout warp
 
     const bool prefix_cached = args.tensors != nullptr && args.count <= kPrefixCap;
@@ -902,7 +948,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         sm.staged_tensor = -1;
         sm.abort = 0;
         sm.gid_taken = 0;
-        for (int i = 0; i < kStages; ++i) {
+        for (int i = 0; i < kMaxStages; ++i) {
             mbar_init(smem_u32(&sm.full_bar[i]), 1u);
             mbar_init(smem_u32(&sm.empty_bar[i]), THREADS / 32);
         }
@@ -910,7 +956,8 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-    if (is_scout) scout_prepare<L, THREADS, CH>(args, sm, ws, 0, prefix_cached, -1);
+    int q_cur = 0, q_end = 0;  // the scout's current grab from the work queue
+    if (is_scout) scout_prepare<L, THREADS, CH>(args, sm, ws, 0, prefix_cached, -1, q_cur, q_end);
     __syncthreads();
 
     bool staged_esc = false;
@@ -922,7 +969,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         if (!P.valid) break;
         if (is_scout) {
             // next item's geometry, row bases and L2 prefetches, while the others decode this one
-            scout_prepare<L, THREADS, CH>(args, sm, ws, slot ^ 1, prefix_cached, iter + 1);
+            scout_prepare<L, THREADS, CH>(args, sm, ws, slot ^ 1, prefix_cached, iter + 1, q_cur, q_end);
         } else if (P.ok) {
             const int ti = P.ti, mode = P.mode;
             const mps_bucket_tensor& T = (args.tensors != nullptr) ? args.tensors[ti] : args.single;
@@ -948,11 +995,12 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                 const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(bucket_bytes) & 15u);  // 0 or 8
                 const long long valid = 8 * (T.bitstream_words - wb) + mis;
                 const long long bits = (long long)P.ebits + 8 * mis;  // end of the bucket's bits from the origin
-                // every chunk a valid sub-stream can ask for (kRingChunks ahead of its last unit) must exist
-                if ((mis == 0u || wb > 0) && valid <= 0x7FFFFFF0LL && (bits >> 3) + 16 * (kRingChunks + 2) <= valid) {
+                // the bucket's own bits must lie inside the bitstream; look-ahead past its end is never copied
+                if ((mis == 0u || wb > 0) && valid >= 16 && valid <= 0x7FFFFFF0LL && ((bits + 7) >> 3) <= valid) {
                     stream = true;
                     it.ctx_bytes = T.ctx_bytes; it.out = T.out; it.startbit = startbit; it.rowbase = rowbase;
                     it.bo.base = bucket_bytes - mis; it.bo.last_ofs = (uint32_t)((valid - 16) & ~15LL); it.bo.bit_delta = 8 * mis;
+                    it.bo.tail_ofs = (valid & 8) ? it.bo.last_ofs + 16u : 0xFFFFFFFFu;
                     it.t_begin = t_begin; it.k_eff = k_eff; it.col_len = (uint32_t)col_len;
                     it.nsteps = (uint32_t)(total / k_eff);
                 }
@@ -962,10 +1010,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             uint32_t nblocks = 0;
             if (stream) nblocks = (it.nsteps + kSS - 1) / kSS;
             if (is_producer) {
-                if (stream) {
-                    uint32_t p_next = 0, p_rr = 0, p_cc = 0;
-                    run_ok = producer_run<SPAN>(sm, it, blk, p_next, p_rr, p_cc, nblocks);
-                }
+                if (stream) run_ok = producer_run<SPAN>(sm, it, blk, nblocks);
             } else if (is_consumer) {
                 if (stream) stream_begin<L, THREADS, CH>(sm, it, st);
                 MPS_TICK(2);  // async copies started
