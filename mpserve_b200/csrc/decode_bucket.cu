@@ -58,6 +58,9 @@ constexpr int kSS = 8;                // steps per stage of the streaming path's
 #ifndef MPS_LOOK
 #define MPS_LOOK 1
 #endif
+#ifndef MPS_COOP_BEGIN
+#define MPS_COOP_BEGIN 1
+#endif
 #ifndef MPS_NO_STREAM
 #define MPS_NO_STREAM 0
 #endif
@@ -546,22 +549,40 @@ struct StreamThread {  // per-thread state that lives from stream_begin to strea
 };
 
 // Start what can overlap with table staging: the first chunks of every sub-stream's bitstream.
+// The four chunks of a sub-stream are 64 contiguous bytes, so four neighbouring lanes fetch them
+// together: one cp.async instruction of a warp then touches 8 cache lines instead of 32, and the
+// load/store unit, which looks lines up one per cycle, gets through an item's first 64 KB four
+// times sooner.  A lane therefore writes into its neighbours' rings; stream_run orders that with
+// cp.async.wait_group followed by __syncwarp before anyone reads.
 template <int L, int THREADS, int CH>
 __device__ __forceinline__ void stream_begin(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st) {
-    const uint32_t tid = threadIdx.x;
-    const uint32_t ring0 = smem_u32(sm.bitring) + tid * kRingBytes;
+    static_assert(kRingChunks == 4, "four lanes share a sub-stream's first chunks");
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp0 = tid & ~31u;
+    const uint32_t rings = smem_u32(sm.bitring);
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-        const uint32_t ring = ring0 + c * THREADS * kRingBytes;
         const uint32_t pos = it.startbit[it.t_begin + tid * CH + c] + it.bo.bit_delta;
         st.ch[c].pos = pos;
-        const uint32_t c0 = pos >> 7;
+        st.ch[c].next = (pos >> 7) + kRingChunks;
+    }
+#if !MPS_COOP_BEGIN
 #pragma unroll
-        for (int q = 0; q < kRingChunks; ++q) {
-            const uint32_t ofs = (c0 + q) << 4;
-            chunk_fetch(ring, it.bo, ofs);
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int q = 0; q < kRingChunks; ++q)
+            chunk_fetch(rings + (c * THREADS + tid) * kRingBytes, it.bo, ((st.ch[c].pos >> 7) + q) << 4);
+    cp_async_commit();
+    return;
+#endif
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t owner = j * 8 + (lane >> 2);  // lane of this warp whose chain c is served
+            const uint32_t pos = __shfl_sync(0xFFFFFFFFu, st.ch[c].pos, owner);
+            const uint32_t ring = rings + (c * THREADS + warp0 + owner) * kRingBytes;
+            chunk_fetch(ring, it.bo, ((pos >> 7) + (lane & 3u)) << 4);
         }
-        st.ch[c].next = c0 + kRingChunks;
     }
     cp_async_commit();
 }
@@ -591,8 +612,9 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
     const uint32_t ctx0 = smem_u32(sm.ctxring) + tid * CH;
     const uint32_t t0 = it.t_begin + tid * CH;
 
-    // first units of every sub-stream (their chunks were requested in stream_begin)
+    // first units of every sub-stream (their chunks were requested in stream_begin by this warp's lanes)
     cp_async_wait<0>();
+    __syncwarp();
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
         const uint32_t ring = ring0 + c * THREADS * kRingBytes;
