@@ -52,7 +52,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 // ------------------------------------------------------------------------------------------------
 constexpr int kTableEntries = 32768;  // 256 ctx x 2^7 == 16 ctx x 2^11
 constexpr int kRowCap = 1024;         // rows / groups of a bucket cached in shared memory
-constexpr int kPrefixCap = 64;        // tensors of a batch whose item prefix is cached in shared memory
+constexpr int kPrefixCap = 16;        // tensors of a batch whose item prefix is cached in shared memory
 constexpr int kSteps = 4;             // steps per software-pipeline block (register-prefetch path)
 constexpr int kSS = 8;                // steps per stage of the streaming path's context ring
 #ifndef MPS_LOOK
@@ -119,6 +119,7 @@ struct Smem {
     uint32_t rowbase[2][kRowCap];                // element offset of each row / group start (0xFFFFFFFF: invalid),
                                                  // one set for the item being decoded, one being prepared
     Prepared prep[2];
+    mps_bucket_tensor tensor[2];                 // descriptor of the item's tensor, copied by the scout
     long long prefix[kPrefixCap + 1];
     unsigned long long full_bar[kMaxStages];     // bulk copies of a stage have landed
     unsigned long long empty_bar[kMaxStages];    // every warp is done reading a stage
@@ -129,6 +130,8 @@ struct Smem {
     int staged_tensor;
     int abort;                                   // a bounded wait gave up
 };
+
+static_assert(sizeof(Smem) <= 227 * 1024, "one CTA per SM: everything must fit the 227 KB a CTA can have");
 
 // Entry layout.  L=7 (FP8): sym << 16 | raw length nibble (bits 0-2 code length, bit 3 = ESC), which a
 // byte permute builds straight from the sidecar's packed arrays.  L=11 (AWQ): sym << 16 | esc << 15 |
@@ -868,7 +871,16 @@ __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws,
         ti = lo;
         local = item - (prefix_cached ? sm.prefix[ti] : args.item_prefix[ti]);
     }
-    const mps_bucket_tensor& T = (args.tensors != nullptr) ? args.tensors[ti] : args.single;
+    // the decoding warps read the descriptor from shared memory: a dependent chain of global loads at
+    // the start of every item would be time nobody decodes in
+    {
+        static_assert(sizeof(mps_bucket_tensor) % 4 == 0, "descriptor is copied word by word");
+        const uint32_t* src = reinterpret_cast<const uint32_t*>((args.tensors != nullptr) ? &args.tensors[ti] : &args.single);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.tensor[slot]);
+        for (int i = lane; i < (int)(sizeof(mps_bucket_tensor) / 4); i += 32) dst[i] = src[i];
+        __syncwarp();
+    }
+    const mps_bucket_tensor& T = sm.tensor[slot];
     const int mode = T.mode;
     const uint32_t k = (uint32_t)T.k;
     const uint32_t chunks = (k + SPAN - 1) / SPAN;
@@ -994,7 +1006,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             scout_prepare<L, THREADS, CH>(args, sm, ws, slot ^ 1, prefix_cached, iter + 1, q_cur, q_end);
         } else if (P.ok) {
             const int ti = P.ti, mode = P.mode;
-            const mps_bucket_tensor& T = (args.tensors != nullptr) ? args.tensors[ti] : args.single;
+            const mps_bucket_tensor& T = sm.tensor[slot];
             const uint32_t k = P.k, k_eff = P.k_eff, t_begin = P.t_begin;
             const long long b = P.b, row_a = P.row_a, nrows = P.nrows, col_start = P.col_start, col_len = P.col_len;
             const long long total = P.total, wb = P.wb;
