@@ -159,6 +159,12 @@ MPS_API int mps_decode_fp8_noalloc(const uint8_t* fp8_u8, const uint64_t* bitstr
  * reference launches one kernel per weight (scripts/mpserve_vllm_fp8_huffman.py:526-543). */
 MPS_API int mps_bucket_batch_plan(const mps_bucket_tensor* tensors_host, int count, int64_t* item_prefix_host,
                           int32_t* threads_out, int32_t* chains_out);
+/* One tensor from a HOST descriptor (device pointers inside), any mode: what the per-format entries
+ * above do after packing their arguments.  A plan gives zero work items to tensors made of tiny
+ * buckets (item_prefix[i+1] == item_prefix[i]); those are decoded with this call instead, by a
+ * kernel that reads the sidecar's tables in place.  No reference counterpart. */
+MPS_API int mps_decode_bucket_tensor(const mps_bucket_tensor* tensor_host, void* workspace, size_t workspace_bytes,
+                                     void* stream);
 MPS_API int mps_decode_bucket_batch(const mps_bucket_tensor* tensors_dev, const int64_t* item_prefix_dev, int count,
                             int64_t total_items, int32_t threads, int32_t chains, int32_t mode,
                             void* workspace, size_t workspace_bytes, void* stream);

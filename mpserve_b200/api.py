@@ -426,6 +426,9 @@ class BucketDecodePlan:
         _lib.check(lib.mps_bucket_batch_plan(descs, count, prefix, C.byref(threads), C.byref(chains)))
         self.count, self.threads, self.chains = count, int(threads.value), int(chains.value)
         self.total_items = int(prefix[count])
+        # tensors of tiny buckets get no work items in the shared launch: each is decoded on its own
+        self._descs_host = descs
+        self._direct = [i for i in range(count) if prefix[i + 1] == prefix[i] and descs[i].num_buckets > 0]
         raw = torch.frombuffer(bytearray(bytes(descs)), dtype=torch.uint8)
         self._descs_dev = raw.to(self.device)
         self._prefix_dev = torch.tensor(list(prefix), dtype=torch.int64).to(self.device)
@@ -433,10 +436,14 @@ class BucketDecodePlan:
     def decode(self) -> list[torch.Tensor]:
         with torch.cuda.device(self.device):
             ws = _workspace(self.device)
-            rc = _lib.load().mps_decode_bucket_batch(
-                self._descs_dev.data_ptr(), self._prefix_dev.data_ptr(), self.count, self.total_items, self.threads,
-                self.chains, self.mode, ws.data_ptr(), ws.numel() * 4, _stream_ptr(self.device))
-        _lib.check(rc)
+            lib = _lib.load()
+            stream = _stream_ptr(self.device)
+            if self.total_items > 0:
+                _lib.check(lib.mps_decode_bucket_batch(
+                    self._descs_dev.data_ptr(), self._prefix_dev.data_ptr(), self.count, self.total_items, self.threads,
+                    self.chains, self.mode, ws.data_ptr(), ws.numel() * 4, stream))
+            for i in self._direct:
+                _lib.check(lib.mps_decode_bucket_tensor(C.byref(self._descs_host[i]), ws.data_ptr(), ws.numel() * 4, stream))
         return self.outputs
 
 

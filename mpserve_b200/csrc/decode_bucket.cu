@@ -1123,6 +1123,70 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
 }
 
 // ------------------------------------------------------------------------------------------------
+// Direct path for tensors made of tiny buckets (AWQ with one bucket per 128-element group, small
+// per-channel weights): staging 128 KB of fused tables per bucket would cost far more than decoding
+// it, so here every sub-stream is one thread that looks its codes up in the sidecar's own tables in
+// global memory (they stay in L2), exactly as the sidecar stores them.  Parallelism comes from the
+// number of sub-streams, which is what such tensors have plenty of.
+// ------------------------------------------------------------------------------------------------
+template <int L>
+__global__ void __launch_bounds__(256) direct_decode_kernel(const __grid_constant__ mps_bucket_tensor T, long long total_sub) {
+    constexpr int NCTX = (L == 7) ? 256 : 16;
+    constexpr int TS = 1 << L;
+    const int mode = T.mode;
+    const long long k = T.k;
+    for (long long w = blockIdx.x * 256LL + threadIdx.x; w < total_sub; w += (long long)gridDim.x * 256LL) {
+        const long long b = w / k;
+        const uint32_t t = (uint32_t)(w - b * k);
+        const long long row_a = T.bucket_row_offsets[b];
+        const long long nrows = (long long)T.bucket_row_offsets[b + 1] - row_a;
+        long long col_start = 0, col_len = T.group_size;
+        if (mode != 2) { col_start = T.bucket_col_start[b]; col_len = T.bucket_col_len[b]; }
+        const long long bit_base = T.bucket_bit_base[b];
+        const long long wb = bit_base >> 6;
+        const bool ok = nrows > 0 && col_len > 0 && row_a >= 0 && row_a + nrows <= T.num_rows &&
+                        (mode == 2 || (col_start >= 0 && col_start + col_len <= T.m)) && bit_base >= 0 && wb < T.bitstream_words;
+        if (!ok) continue;
+        const long long total = nrows * col_len;
+        const uint32_t k_eff = (total < k) ? (uint32_t)total : (uint32_t)k;
+        if (t >= k_eff) continue;
+        const uint32_t* bs32 = reinterpret_cast<const uint32_t*>(T.bitstream) + 2 * wb;
+        const long long units = 2 * (T.bitstream_words - wb);
+        const uint32_t lim = (uint32_t)((units > 0x7FFFFFFELL ? 0x7FFFFFFELL : units) - 1);
+        const int32_t* btab = T.bucket_table + b * NCTX;
+        BitWin win;
+        win_init(win, bs32, lim, T.thread_startbit[b * (k + 1) + t]);
+        for (long long e = t; e < total; e += k_eff) {
+            const long long rr = e / col_len, cc = e - rr * col_len;
+            const long long row = T.row_indices[row_a + rr];
+            const long long c0 = (mode == 2) ? (long long)T.group_col_start[row_a + rr] : col_start;
+            const bool good = row >= 0 && row < T.n && c0 >= 0 && c0 + col_len <= T.m;
+            const long long idx = row * T.m + c0 + cc;
+            const uint32_t ctx = good ? ctx_of<L>(T.ctx_bytes[idx]) : 0u;
+            int32_t gid = btab[ctx];
+            if (gid >= T.num_tables) gid = -1;
+            const uint32_t peek = win.hi >> (32 - L);
+            uint32_t sym = 0, len = 0, esc = 0;
+            if (gid >= 0) {
+                const uint32_t nib = (__ldg(T.decode_lens + (long long)gid * (TS / 2) + (peek >> 1)) >> ((peek & 1u) * 4u)) & 0xFu;
+                sym = __ldg(T.decode_syms + (long long)gid * TS + peek);
+                if constexpr (L == 7) { len = nib & 7u; esc = nib & 8u; }
+                else { esc = (nib == 15u); len = esc ? (uint32_t)L : nib; }
+            } else if constexpr (L != 7) {
+                esc = 1u; len = (uint32_t)L;  // AWQ: a context without a table reads as an ESC
+            }
+            win_consume(win, len);
+            if (esc) {
+                sym = win.hi >> 16;
+                win_consume(win, 16);
+            }
+            if (good) T.out[idx] = (uint16_t)sym;
+            if (win.avail <= 32) win_refill(win, bs32, lim);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
 static int sm_count() {
@@ -1209,11 +1273,38 @@ static int validate_tensor(const mps_bucket_tensor& T, int L) {
     return MPS_OK;
 }
 
+// Tensors whose sub-streams hold this few symbols (on average) are decoded by the direct kernel.  It
+// pays about ten times more per symbol of a sub-stream than the persistent kernel, whose fixed cost
+// per bucket is worth about ten such symbols: that is the break-even.
+constexpr long long kDirectMaxSteps = 8;
+
+static bool use_direct(const mps_bucket_tensor& T) {
+    const int forced = env_int("MPS_DECODE_DIRECT", -1);
+    if (forced >= 0) return forced != 0;
+    if (T.num_buckets <= 0) return false;
+    const long long per_bucket = (T.n * T.m) / T.num_buckets;
+    const long long k_eff = per_bucket < T.k ? (per_bucket > 0 ? per_bucket : 1) : T.k;
+    return per_bucket / k_eff <= kDirectMaxSteps;
+}
+
+static int decode_direct(const mps_bucket_tensor& T, int L, void* stream) {
+    const long long total_sub = T.num_buckets * (long long)T.k;
+    long long blocks = (total_sub + 255) / 256;
+    const long long cap = 16LL * sm_count();
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (L == 7) direct_decode_kernel<7><<<(unsigned)blocks, 256, 0, st>>>(T, total_sub);
+    else direct_decode_kernel<11><<<(unsigned)blocks, 256, 0, st>>>(T, total_sub);
+    MPS_CUDA_TRY(cudaGetLastError());
+    return MPS_OK;
+}
+
 static int decode_single(const mps_bucket_tensor& T, int L, void* workspace, size_t workspace_bytes, void* stream) {
     int rc = validate_tensor(T, L);
     if (rc) return rc;
     if (!workspace || workspace_bytes < mps_workspace_bytes()) { set_error("workspace missing or too small"); return MPS_ERR_WORKSPACE; }
     if (T.num_buckets == 0) return MPS_OK;
+    if (use_direct(T)) return decode_direct(T, L, stream);
     int threads, chains;
     pick_config(T.num_buckets * (long long)T.k, T.k, &threads, &chains);
     const long long chunks = ((long long)T.k + (long long)threads * chains - 1) / ((long long)threads * chains);
@@ -1401,6 +1492,7 @@ int mps_bucket_batch_plan(const mps_bucket_tensor* tensors_host, int count, int6
     for (int i = 0; i < count; ++i) {
         int rc = validate_tensor(tensors_host[i], L);
         if (rc) return rc;
+        if (use_direct(tensors_host[i])) continue;  // decoded on its own (mps_decode_bucket_tensor)
         subs += tensors_host[i].num_buckets * (long long)tensors_host[i].k;
         if (tensors_host[i].k < k_min) k_min = tensors_host[i].k;
     }
@@ -1410,13 +1502,18 @@ int mps_bucket_batch_plan(const mps_bucket_tensor* tensors_host, int count, int6
     for (int i = 0; i < count; ++i) {
         item_prefix_host[i] = acc;
         const long long span = (long long)threads * chains;
-        acc += tensors_host[i].num_buckets * ((tensors_host[i].k + span - 1) / span);
+        if (!use_direct(tensors_host[i])) acc += tensors_host[i].num_buckets * ((tensors_host[i].k + span - 1) / span);
     }
     item_prefix_host[count] = acc;
     if (acc > 0x7FFFFFF0LL) { set_error("too many work items"); return MPS_ERR_INVALID; }
     *threads_out = threads;
     *chains_out = chains;
     return MPS_OK;
+}
+
+int mps_decode_bucket_tensor(const mps_bucket_tensor* tensor_host, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!tensor_host) { set_error("mps_decode_bucket_tensor: null descriptor"); return MPS_ERR_INVALID; }
+    return decode_single(*tensor_host, tensor_host->mode == 0 ? 7 : 11, workspace, workspace_bytes, stream);
 }
 
 int mps_decode_bucket_batch(const mps_bucket_tensor* tensors_dev, const int64_t* item_prefix_dev, int count,

@@ -95,7 +95,7 @@ def awq_case(name: str, n: int, m: int, layout: str, k: int, seed: int, dev, flu
                                                                                 threads=k, group_cap=1024)
         keys = _BYSCALE_KEYS
         a = [art[key] for key in keys]
-        gs = int(art["group_size"])
+        gs = int(art["shape_nmkg_i64"][3])
 
         def run():
             return MPServe_cuda.huffman_decode_awq_int4_bucket_by_scale(c.int4_u8, *a, n, m, 11, gs)

@@ -27,8 +27,15 @@ def dev():
 
 @pytest.fixture
 def force_config():
+    """Pin the decode path: ("direct",) = the per-sub-stream kernel that reads the tables in place,
+    (threads, chains) = the persistent kernel in that shape, nothing = the library's own choice."""
     def _set(threads=None, chains=None):
-        for k, v in (("MPS_DECODE_THREADS", threads), ("MPS_DECODE_CHAINS", chains)):
+        direct = None
+        if threads == "direct":
+            threads, direct = None, 1
+        elif threads is not None:
+            direct = 0
+        for k, v in (("MPS_DECODE_THREADS", threads), ("MPS_DECODE_CHAINS", chains), ("MPS_DECODE_DIRECT", direct)):
             if v is None:
                 os.environ.pop(k, None)
             else:
@@ -36,6 +43,9 @@ def force_config():
 
     yield _set
     _set(None, None)
+
+
+DIRECT = ("direct", None)
 
 
 def _u16(t):
@@ -69,7 +79,7 @@ def _encode_golden(g):
 # ---------------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("name", golden_names("fp8"))
-@pytest.mark.parametrize("cfg", [None, (256, 4), (512, 1), (128, 8)])
+@pytest.mark.parametrize("cfg", [None, DIRECT, (256, 4), (512, 1), (128, 8)], ids=str)
 def test_fp8_golden(golden_cases, dev, force_config, name, cfg):
     g = golden_cases[name]
     art = _encode_golden(g)
@@ -105,7 +115,7 @@ def test_fp8_seeded_all_configs(dev, force_config, case):
     art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, k)
     want = orc.decode_fp8(c.fp8_u8.numpy(), art, n, m)
     np.testing.assert_array_equal(want, _u16(c.bf16))
-    for cfg in [None] + CONFIGS:
+    for cfg in [None, DIRECT] + CONFIGS:
         force_config(*(cfg or (None, None)))
         got = _fp8_decode(c.fp8_u8.numpy(), art, n, m, dev)
         np.testing.assert_array_equal(got, want, err_msg=f"config {cfg}")
@@ -117,7 +127,7 @@ def test_fp8_esc_large(dev, force_config):
     c = wl.quantize_fp8(wl.random_weight(n, m, 7, "student_t"), "tensor")
     art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
     assert ((art["decode_lens_u8"] & 0x88) != 0).any(), "case was meant to contain ESC tables"
-    for cfg in (None, (256, 4), (512, 2), (256, 1)):
+    for cfg in (None, DIRECT, (256, 4), (512, 2), (256, 1)):
         force_config(*(cfg or (None, None)))
         got = _fp8_decode(c.fp8_u8.numpy(), art, n, m, dev)
         np.testing.assert_array_equal(got, _u16(c.bf16), err_msg=f"config {cfg}")
@@ -140,19 +150,22 @@ def test_fp8_repeated_calls_reuse_workspace(dev):
         np.testing.assert_array_equal(_fp8_decode(c.fp8_u8.numpy(), art, n, m, dev), _u16(c.bf16))
 
 
-def test_fp8_missing_table_decodes_zero(dev):
+@pytest.mark.parametrize("cfg", [DIRECT, (256, 1)], ids=str)
+def test_fp8_missing_table_decodes_zero(dev, force_config, cfg):
     """A context without a table (gid = -1) yields zeros and consumes nothing, as in the reference
     kernel (decode_huffman.cu:252-264); the oracle does the same."""
     n, m = 64, 256
     c = wl.quantize_fp8(wl.random_weight(n, m, 5, "normal"), "tensor")
     art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 256)
     art["bucket_table_i32"][:, 0x30:0x38] = -1
+    force_config(*cfg)
     want = orc.decode_fp8(c.fp8_u8.numpy(), art, n, m)
     got = _fp8_decode(c.fp8_u8.numpy(), art, n, m, dev)
     np.testing.assert_array_equal(got, want)
 
 
-def test_fp8_corrupt_metadata_is_contained(dev):
+@pytest.mark.parametrize("cfg", [DIRECT, (256, 1)], ids=str)
+def test_fp8_corrupt_metadata_is_contained(dev, force_config, cfg):
     """Out-of-range rows / windows / offsets must not fault: such buckets are skipped or clamped."""
     n, m = 64, 256
     c = wl.quantize_fp8(wl.random_weight(n, m, 6, "normal"), "channel")
@@ -164,6 +177,7 @@ def test_fp8_corrupt_metadata_is_contained(dev):
     bad["bucket_col_len_i32"][-1] = m + 7
     bad["bucket_thread_startbit_u32"] = art["bucket_thread_startbit_u32"].copy()
     bad["bucket_thread_startbit_u32"][1, :] = 0xFFFFFF00
+    force_config(*cfg)
     _fp8_decode(c.fp8_u8.numpy(), bad, n, m, dev)  # completes; content of the bad buckets is unspecified
     # the context is still healthy afterwards
     np.testing.assert_array_equal(_fp8_decode(c.fp8_u8.numpy(), art, n, m, dev), _u16(c.bf16))
@@ -193,7 +207,10 @@ def test_fp8_argument_validation(dev):
 
 
 def test_fp8_batch_plan_matches_single(dev):
-    shapes = [(256, 1024, "channel"), (64, 512, "tensor"), (1024, 256, "channel"), (8, 4096, "channel")]
+    # per-channel tensors of this size have tiny buckets (decoded one by one, in place); the per-tensor
+    # ones have full 128-row buckets and share the persistent launch
+    shapes = [(256, 1024, "channel"), (512, 512, "tensor"), (1024, 256, "channel"), (8, 4096, "channel"),
+              (1024, 2048, "tensor")]
     entries, wants = [], []
     for i, (n, m, mode) in enumerate(shapes):
         c = wl.quantize_fp8(wl.random_weight(n, m, 40 + i, "normal"), mode)
@@ -201,6 +218,7 @@ def test_fp8_batch_plan_matches_single(dev):
         entries.append((c.fp8_u8.to(dev), util.artifacts_to_device(art, dev), None))
         wants.append(_u16(c.bf16))
     plan = api.BucketDecodePlan(entries, mode=0)
+    assert plan._direct and plan.total_items > 0, "the case was meant to exercise both kernels"
     for _ in range(2):
         outs = plan.decode()
         torch.cuda.synchronize()
@@ -242,8 +260,10 @@ def _awq_decode(kind, ctx_np, art, n, m, dev, L=11):
 
 
 @pytest.mark.parametrize("name", golden_names("awq"))
-def test_awq_golden(golden_cases, dev, name):
+@pytest.mark.parametrize("cfg", [DIRECT, (256, 1)], ids=str)
+def test_awq_golden(golden_cases, dev, force_config, name, cfg):
     g = golden_cases[name]
+    force_config(*cfg)
     art = _encode_golden(g)
     g.check_artifacts(art)
     n, m = g.bf16.shape
@@ -267,7 +287,7 @@ def test_awq_seeded(dev, force_config, scale_kind):
         "awq_shared": orc.build_awq_shared(b, q, sc, 11),
     }
     for kind, art in arts.items():
-        for cfg in (None, (256, 1), (128, 4)):
+        for cfg in (None, DIRECT, (256, 1), (128, 4)):
             force_config(*(cfg or (None, None)))
             got = _awq_decode(kind, q, art, n, m, dev)
             np.testing.assert_array_equal(got, b, err_msg=f"{kind} {cfg}")
