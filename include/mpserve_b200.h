@@ -183,6 +183,7 @@ MPS_API int mps_decode_bucket_batch(const mps_bucket_tensor* tensors_dev, const 
  *   rect_layout  fills bucket_thread_startbit [B,k+1] and bucket_bit_base [B+1], returns total bits
  *   rect_emit    fills bitstream_u64 [(total_bits+63)/64]
  * variant: 0 FP8 (context = fp8 byte), 1 AWQ-INT4 rectangular buckets (context = int4 code),
+ *          3 AWQ-INT4 shared tables (analysis only; continue with the mps_build_shared_* calls below),
  *          2 AWQ-INT4 ragged buckets by exact scale (huffman_build_awq_int4_bucket_decode_tables_by_scale_entry,
  *            kernel/build_huffman.cu:1074-1580; wrapper.cpp:290-321): pass bucket_col_len = NULL, the groups'
  *            rows as row_indices, their column starts as bucket_col_start and the group offsets as
@@ -215,6 +216,27 @@ MPS_API int mps_build_rect_emit(mps_build_state* state, const uint16_t* bf16_bit
                                 const int32_t* row_indices_i32, int64_t num_buckets, int32_t k,
                                 const uint32_t* bucket_thread_startbit_u32, const int64_t* bucket_bit_base_i64,
                                 uint64_t* bitstream_u64, int64_t bitstream_words, void* stream);
+
+/* Shared-table sidecar (huffman_build_awq_decode_tables_entry, build_huffman.cu:2157-2633):
+ * mps_build_analyze with variant 3, then these three.  sid_lut_i32: DEVICE int32[65536], the dense id
+ * of every scale value that occurs (ascending by value), -1 elsewhere; num_scales = S.
+ *   codebooks: decode_syms_i16 / decode_nbits_u8 [S*16, 2^max_len], one table per (scale id, int4 code)
+ *              stream whether it occurs or not; whole-byte lengths, bit 7 marks an ESC slot (:2311-2428)
+ *   layout:    scale_bit_base_i64 [S+1] (device) and, returned to the host, the chunk count and the total
+ *              bits; chunks are runs of <= 255 consecutive elements of one stream (:2434-2537)
+ *   emit:      bitstream (every scale's bits in flat element order, 64-bit aligned), the four chunk
+ *              arrays [C], out_idx_i32 [numel] (identity, :2586-2588), the stream -> chunk CSR (:2590-2610) */
+MPS_API int mps_build_shared_codebooks(mps_build_state* state, const int32_t* sid_lut_i32, int64_t num_scales,
+                                       int16_t* decode_syms_i16, uint8_t* decode_nbits_u8, void* stream);
+MPS_API int mps_build_shared_layout(mps_build_state* state, const uint16_t* bf16_bits, const uint8_t* int4_u8,
+                                    const uint16_t* scales_u16, int32_t scale_mode, int64_t nb1, int64_t sb0, int64_t sb1,
+                                    const int32_t* sid_lut_i32, int64_t* scale_bit_base_i64, void* stream,
+                                    int64_t* num_chunks_out, int64_t* total_bits_out);
+MPS_API int mps_build_shared_emit(mps_build_state* state, const uint16_t* bf16_bits, const int64_t* scale_bit_base_i64,
+                                  uint64_t* bitstream_u64, int64_t bitstream_words, uint32_t* chunk_startbit_rel_u32,
+                                  uint32_t* chunk_out_base_u32, uint32_t* chunk_meta_u32, int32_t* chunk_scale_id_i32,
+                                  int32_t* out_idx_i32, int64_t* stream_chunk_ofs_i64, int32_t* stream_chunk_ids_i32,
+                                  void* stream);
 
 /* Checksum of a decoded tensor: sum of the 16-bit patterns (mod 2^64) and an XOR fold of
  * (pattern * (index+1)) -- what ranks all-reduce after a sharded decode.  result_dev: device

@@ -59,6 +59,10 @@ _PROTOS = {
     "mps_build_bucket_unique": (C.c_int, [_p, _i64, _p, _p, _p, _p]),
     "mps_build_rect_layout": (C.c_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i32, _p, _p, _p, C.POINTER(_i64)]),
     "mps_build_rect_emit": (C.c_int, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i32, _p, _p, _p, _i64, _p]),
+    "mps_build_shared_codebooks": (C.c_int, [_p, _p, _i64, _p, _p, _p]),
+    "mps_build_shared_layout": (C.c_int, [_p, _p, _p, _p, _i32, _i64, _i64, _i64, _p, _p, _p, C.POINTER(_i64),
+                                          C.POINTER(_i64)]),
+    "mps_build_shared_emit": (C.c_int, [_p, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _p]),
 }
 
 _lib = None

@@ -46,6 +46,10 @@ struct BuildState {
     size_t o_scratch;          // start of the reusable scratch area
     size_t scratch_bytes;
     int32_t* d_flag;           // device error flag (first word of ws)
+    // shared-table layout only (carved from the scratch area by the shared-table calls)
+    int64_t num_scales, num_chunks;
+    size_t o_sh_keep;          // start of what the layout call leaves for the emit call
+    size_t o_sh_end;           // end of it
 };
 static_assert(sizeof(BuildState) <= 256, "mps_build_state is 256 bytes");
 
@@ -185,21 +189,26 @@ __global__ void codebook_kernel(const unsigned long long* __restrict__ items, co
                                 const int* __restrict__ ctx_ofs, const int* __restrict__ perm, long long g0, long long g1,
                                 int L, int variant, CbScratch S, uint16_t* __restrict__ out_syms,
                                 uint8_t* __restrict__ out_lens, uint32_t* __restrict__ enc, uint32_t* __restrict__ esc,
-                                uint16_t* __restrict__ escsym, int* __restrict__ err) {
+                                uint16_t* __restrict__ escsym, int* __restrict__ err, const int* __restrict__ row_of) {
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
     const long long g = g0 + s;
     if (g >= g1 || s >= S.chunk) return;
     const int TS = 1 << L;
     const int a = ctx_ofs[g], b = ctx_ofs[g + 1], cnt = b - a;
-    uint16_t* tsym = out_syms + g * TS;
-    uint8_t* tlen = out_lens + g * (TS / 2);
+    // shared-table sidecars keep one table per (scale id, context) stream, present or not, and whole-byte
+    // lengths; the bucket formats keep one table per context that occurs, lengths packed two per byte
+    const bool bytes = (variant == V_AWQ_SHARED);
+    const long long row = row_of ? row_of[g] : g;
+    uint16_t* tsym = out_syms + row * TS;
+    uint8_t* tlen = out_lens + (bytes ? row * TS : row * (TS / 2));
     esc[g] = 0;
     escsym[g] = 0;
     if (cnt <= 0) return;
     if (cnt == 1) {  // single symbol: length 1, code 0, every slot (build_huffman.cu:464-472)
         const uint16_t sy = (uint16_t)(items[a] & 0xFFFF);
         for (int i = 0; i < TS; ++i) tsym[i] = sy;
-        for (int i = 0; i < TS / 2; ++i) tlen[i] = 0x11;
+        if (bytes) for (int i = 0; i < TS; ++i) tlen[i] = 1;
+        else for (int i = 0; i < TS / 2; ++i) tlen[i] = 0x11;
         enc[a] = (1u << 16);
         return;
     }
@@ -234,7 +243,8 @@ __global__ void codebook_kernel(const unsigned long long* __restrict__ items, co
         }
         esc_sym = (uint16_t)(cand <= 0xFFFFu ? cand : 0xFFFFu);
         int esc_i = (int)esc_w;                        // the reference accumulates in int
-        if (variant == V_AWQ_BUCKET && esc_i <= 0) esc_i = 1;
+        if (variant == V_AWQ_SHARED) esc_i = esc_w > 2147483647LL ? 2147483647 : (int)esc_w;  // (:2345-2352)
+        if ((variant == V_AWQ_BUCKET || variant == V_AWQ_SHARED) && esc_i <= 0) esc_i = 1;
         n = 0;
         bool placed = false;
         if (variant == V_AWQ_BYSCALE) {
@@ -285,7 +295,7 @@ __global__ void codebook_kernel(const unsigned long long* __restrict__ items, co
         }
     }
     if (!package_merge_device(S, s, n, L)) { atomicExch(err, 2); return; }
-    if (use_esc && variant != V_FP8) AT(S.len, esc_pos) = (uint8_t)L;  // ESC code forced to L bits (:1812-1816)
+    if (use_esc && (variant == V_AWQ_BUCKET || variant == V_AWQ_BYSCALE)) AT(S.len, esc_pos) = (uint8_t)L;  // ESC code forced to L bits (:1812-1816)
 
     // canonical codes handed out in item order within each length (build_huffman.cu:171-203)
     uint32_t next_code[17];
@@ -308,12 +318,19 @@ __global__ void codebook_kernel(const unsigned long long* __restrict__ items, co
         const uint32_t base = code << (L - len), fill = 1u << (L - len);
         for (uint32_t t = 0; t < fill; ++t) {
             const uint32_t idx = base + t;
-            if (idx < (uint32_t)TS) { tsym[idx] = sy; set_nibble(tlen, idx, nib); }
+            if (idx < (uint32_t)TS) {
+                tsym[idx] = sy;
+                if (bytes) tlen[idx] = (uint8_t)len; else set_nibble(tlen, idx, nib);
+            }
         }
     }
-    if (use_esc && variant != V_FP8) {  // every slot that shows the ESC symbol is marked 15 (:1822-1829)
+    if (use_esc && (variant == V_AWQ_BUCKET || variant == V_AWQ_BYSCALE)) {  // every slot that shows the ESC symbol is marked 15 (:1822-1829)
         for (int i = 0; i < TS; ++i)
             if (tsym[i] == esc_sym) set_nibble(tlen, i, 15u);
+    }
+    if (use_esc && bytes) {             // shared tables mark them with bit 7 (:2410-2415)
+        for (int i = 0; i < TS; ++i)
+            if (tsym[i] == esc_sym) tlen[i] = (uint8_t)(tlen[i] | 0x80u);
     }
 #undef AT
 }
@@ -502,6 +519,164 @@ __global__ void table_keys_kernel(const uint32_t* __restrict__ ctx_key, long lon
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// shared-table layout (build_huffman.cu:2157-2633): one stream per (scale id, context), present or
+// not; one bitstream per scale holding its elements in flat order; chunks of at most 255 consecutive
+// elements of one stream
+// ------------------------------------------------------------------------------------------------
+__global__ void shared_rows_kernel(const uint32_t* __restrict__ ctx_key, long long G, const int32_t* __restrict__ sid_lut,
+                                   int* __restrict__ row_of, int* __restrict__ stream_ctx) {
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= G) return;
+    const uint32_t key = ctx_key[g];
+    const int sid = sid_lut[key >> 16];
+    const int row = sid * 16 + (int)(key & 0xFu);
+    row_of[g] = row;
+    stream_ctx[row] = (int)g;
+}
+
+// per element: its stream, its code (len << 16 | code, bit 31: 16 raw bits follow) and its bit count
+__global__ void shared_elem_kernel(const uint16_t* __restrict__ sym, const uint8_t* __restrict__ q,
+                                   const uint16_t* __restrict__ scales, int scale_mode, long long m, long long nb1,
+                                   long long sb0, long long sb1, const int32_t* __restrict__ sid_lut,
+                                   const int* __restrict__ stream_ctx, CodeBook cb, long long numel,
+                                   int* __restrict__ stream, uint32_t* __restrict__ lc, int* __restrict__ nbits,
+                                   int* __restrict__ run_head, int* __restrict__ err) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= numel) return;
+    auto stream_at = [&](long long e) -> int {
+        uint16_t sc;
+        if (scale_mode == 0) sc = scales[0];
+        else {
+            const long long r = e / m, c = e - r * m;
+            sc = (scale_mode == 1) ? scales[r] : scales[(r / sb0) * nb1 + (c / sb1)];
+        }
+        return sid_lut[sc] * 16 + (int)(q[e] & 0xFu);
+    };
+    const int st = stream_at(i);
+    stream[i] = st;
+    run_head[i] = (i == 0 || stream_at(i - 1) != st) ? (int)i : 0;
+    const int gid = stream_ctx[st];
+    uint32_t code = 0; int len = 0; bool raw = false;
+    const int nb = (gid >= 0) ? element_code(cb, gid, sym[i], code, len, raw) : -1;
+    if (nb < 0) { atomicExch(err, 3); lc[i] = 0; nbits[i] = 0; return; }
+    lc[i] = ((uint32_t)len << 16) | code | (raw ? 0x80000000u : 0u);
+    nbits[i] = nb;
+}
+
+__global__ void shared_chunk_heads_kernel(const int* __restrict__ run_start, long long numel, int* __restrict__ chead) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < numel) chead[i] = ((i - run_start[i]) % 255 == 0) ? 1 : 0;
+}
+
+__global__ void shared_sid_keys_kernel(const int* __restrict__ stream, long long numel, int* __restrict__ key, int* __restrict__ val) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < numel) { key[i] = stream[i] >> 4; val[i] = (int)i; }
+}
+
+__global__ void gather_i32_kernel(const int* __restrict__ src, const int* __restrict__ idx, long long N, int* __restrict__ dst) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < N) dst[i] = src[idx[i]];
+}
+
+// in scale-sorted order: where every scale's run starts and how many bits it holds
+__global__ void shared_segments_kernel(const int* __restrict__ sid_sorted, const int* __restrict__ nb_sorted,
+                                       const unsigned long long* __restrict__ cum, long long numel,
+                                       unsigned long long* __restrict__ seg_base, unsigned long long* __restrict__ seg_bits_end) {
+    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= numel) return;
+    const int sid = sid_sorted[j];
+    if (j == 0 || sid_sorted[j - 1] != sid) seg_base[sid] = cum[j] - (unsigned long long)nb_sorted[j];
+    if (j == numel - 1 || sid_sorted[j + 1] != sid) seg_bits_end[sid] = cum[j];
+}
+
+__global__ void shared_relpos_kernel(const int* __restrict__ sid_sorted, const int* __restrict__ idx_sorted,
+                                     const int* __restrict__ nb_sorted, const unsigned long long* __restrict__ cum,
+                                     const unsigned long long* __restrict__ seg_base, long long numel,
+                                     uint32_t* __restrict__ rel) {
+    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= numel) return;
+    rel[idx_sorted[j]] = (uint32_t)(cum[j] - (unsigned long long)nb_sorted[j] - seg_base[sid_sorted[j]]);
+}
+
+// scale_bit_base: every scale's bitstream starts on a 64-bit boundary (:2543-2560); res[0] = total bits
+__global__ void shared_bases_kernel(const unsigned long long* __restrict__ seg_base, const unsigned long long* __restrict__ seg_end,
+                                    long long S, long long* __restrict__ scale_bit_base, long long* __restrict__ res) {
+    if (blockIdx.x != 0 || threadIdx.x != 0) return;
+    long long total = 0;
+    for (long long s = 0; s < S; ++s) {
+        total = (total + 63) & ~63LL;
+        scale_bit_base[s] = total;
+        total += (long long)(seg_end[s] - seg_base[s]);
+    }
+    total = (total + 63) & ~63LL;
+    scale_bit_base[S] = total;
+    res[0] = total;
+}
+
+__global__ void shared_chunk_pos_kernel(const int* __restrict__ chead, const int* __restrict__ cidx, long long numel,
+                                        long long C, int* __restrict__ cpos) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < numel && chead[i]) cpos[cidx[i]] = (int)i;
+    if (i == 0) cpos[C] = (int)numel;
+}
+
+__global__ void shared_chunk_fill_kernel(const int* __restrict__ cpos, long long C, const int* __restrict__ stream,
+                                         const uint32_t* __restrict__ rel, uint32_t* __restrict__ c_start,
+                                         uint32_t* __restrict__ c_base, uint32_t* __restrict__ c_meta,
+                                         int32_t* __restrict__ c_sid, int* __restrict__ c_stream) {
+    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int i = cpos[c];
+    const int st = stream[i];
+    c_base[c] = (uint32_t)i;
+    c_start[c] = rel[i];
+    c_sid[c] = st >> 4;
+    c_meta[c] = ((uint32_t)(cpos[c + 1] - i) << 8) | (uint32_t)(st & 15);
+    c_stream[c] = st;
+}
+
+__global__ void shared_emit_kernel(const uint16_t* __restrict__ sym, const int* __restrict__ stream,
+                                   const uint32_t* __restrict__ lc, const uint32_t* __restrict__ rel,
+                                   const long long* __restrict__ scale_bit_base, long long numel,
+                                   unsigned long long* __restrict__ bitstream) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= numel) return;
+    const uint32_t v = lc[i];
+    const int len = (int)((v >> 16) & 0x7FFFu);
+    const bool raw = (v >> 31) != 0;
+    unsigned long long bits = v & 0xFFFFu;
+    int nb = len;
+    if (raw) { bits = (bits << 16) | sym[i]; nb += 16; }
+    if (nb <= 0) return;
+    const long long pos = scale_bit_base[stream[i] >> 4] + (long long)rel[i];
+    const long long w = pos >> 6;
+    const int o = (int)(pos & 63);
+    if (o + nb <= 64) atomicOr(&bitstream[w], bits << (64 - o - nb));
+    else {
+        const int second = o + nb - 64;
+        atomicOr(&bitstream[w], bits >> second);
+        atomicOr(&bitstream[w + 1], bits << (64 - second));
+    }
+}
+
+__global__ void shared_stream_ofs_kernel(const int* __restrict__ keys_sorted, long long C, long long num_streams,
+                                         long long* __restrict__ ofs) {
+    const long long s = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (s > num_streams) return;
+    long long lo = 0, hi = C;  // first chunk whose stream is >= s
+    while (lo < hi) {
+        const long long mid = (lo + hi) >> 1;
+        if (keys_sorted[mid] < s) lo = mid + 1; else hi = mid;
+    }
+    ofs[s] = lo;
+}
+
+__global__ void iota_i32_kernel(int32_t* __restrict__ p, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = (int32_t)i;
+}
+
 }  // namespace mps
 
 // ------------------------------------------------------------------------------------------------
@@ -553,7 +728,7 @@ int mps_build_analyze(mps_build_state* state, const uint16_t* bf16_bits, const u
         return MPS_ERR_INVALID;
     }
     if (n <= 0 || m <= 0) { set_error("bf16_params shape must be non-empty"); return MPS_ERR_INVALID; }
-    if (variant != V_FP8 && variant != V_AWQ_BUCKET && variant != V_AWQ_BYSCALE) { set_error("this builder variant is not implemented on the GPU yet"); return MPS_ERR_UNSUPPORTED; }
+    if (variant < V_FP8 || variant > V_AWQ_SHARED) { set_error("unknown builder variant %d", variant); return MPS_ERR_INVALID; }
     if (max_len <= 0 || max_len > 15) { set_error("max_len must be in [1, 15]"); return MPS_ERR_INVALID; }
     if (scale_mode < 0 || scale_mode > 2 || (scale_mode == 2 && (nb1 <= 0 || sb0 <= 0 || sb1 <= 0))) {
         set_error("unsupported scales layout");
@@ -645,6 +820,7 @@ int mps_build_codebooks(mps_build_state* state, uint16_t* decode_syms_u16, uint8
         return MPS_ERR_INVALID;
     }
     BuildState& S = *state_of(state);
+    if (S.variant == V_AWQ_SHARED) { set_error("shared-table sidecars use mps_build_shared_codebooks"); return MPS_ERR_INVALID; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int L = S.L;
     const size_t TS = 1ull << L, KEEP = 4 * (TS - 1);
@@ -678,7 +854,7 @@ int mps_build_codebooks(mps_build_state* state, uint16_t* decode_syms_u16, uint8
         const long long g1 = (g0 + chunk < S.G) ? g0 + chunk : S.G;
         codebook_kernel<<<(int)((g1 - g0 + 63) / 64), 64, 0, st>>>(items, counts, ctx_ofs, perm, g0, g1, L, S.variant, cs,
                                                                     decode_syms_u16, decode_lens_u8, enc, esc, escsym,
-                                                                    S.d_flag);
+                                                                    S.d_flag, nullptr);
     }
     table_keys_kernel<<<grid_for(S.G), 256, 0, st>>>(ctx_key, S.G, table_scale_u16, table_ctx_u16);
     MPS_CUDA_TRY(cudaGetLastError());
@@ -797,5 +973,195 @@ int mps_build_rect_emit(mps_build_state* state, const uint16_t* bf16_bits, const
     MPS_CUDA_TRY(cudaGetLastError());
     return MPS_OK;
 }
+
+// ---- shared-table layout -----------------------------------------------------------------------
+
+int mps_build_shared_codebooks(mps_build_state* state, const int32_t* sid_lut_i32, int64_t num_scales,
+                               int16_t* decode_syms_i16, uint8_t* decode_nbits_u8, void* stream) {
+    if (!state || !sid_lut_i32 || !decode_syms_i16 || !decode_nbits_u8 || num_scales <= 0) {
+        set_error("mps_build_shared_codebooks: bad argument");
+        return MPS_ERR_INVALID;
+    }
+    BuildState& S = *state_of(state);
+    if (S.variant != V_AWQ_SHARED) { set_error("state was not analyzed for the shared-table layout"); return MPS_ERR_INVALID; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int L = S.L;
+    const size_t TS = 1ull << L, KEEP = 4 * (TS - 1);
+    const long long num_streams = num_scales * 16;
+    S.num_scales = num_scales;
+    Carver C{S.ws, S.o_scratch, S.ws_bytes};
+    auto* row_of = C.take<int>(S.G);
+    auto* stream_ctx = C.take<int>(num_streams);
+    S.o_sh_keep = (uint8_t*)row_of - S.ws;
+    S.o_sh_end = align_up(C.off);
+    const size_t slot = codebook_slot_bytes(L);
+    long long chunk = (long long)((kCodebookScratch - (1 << 16)) / slot);
+    if (chunk > S.G) chunk = S.G;
+    if (chunk < 1) { set_error("codebook scratch too small for max_len=%d", L); return MPS_ERR_WORKSPACE; }
+    chunk = (chunk / 32) * 32 > 0 ? (chunk / 32) * 32 : chunk;
+    CbScratch cs;
+    cs.chunk = (int)chunk;
+    cs.w = C.take<unsigned long long>(TS * chunk);
+    cs.cur = C.take<unsigned long long>(KEEP * chunk);
+    cs.nxt = C.take<unsigned long long>(KEEP * chunk);
+    cs.src = C.take<int>(TS * chunk);
+    cs.sym = C.take<uint16_t>(TS * chunk);
+    cs.flag = C.take<uint8_t>((size_t)L * KEEP * chunk);
+    cs.len = C.take<uint8_t>(TS * chunk);
+    if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
+    auto* items = reinterpret_cast<unsigned long long*>(S.ws + S.o_items);
+    auto* counts = reinterpret_cast<int*>(S.ws + S.o_counts);
+    auto* ctx_ofs = reinterpret_cast<int*>(S.ws + S.o_ctx_ofs);
+    auto* ctx_key = reinterpret_cast<uint32_t*>(S.ws + S.o_ctx_key);
+    auto* perm = reinterpret_cast<int*>(S.ws + S.o_perm);
+    auto* enc = reinterpret_cast<uint32_t*>(S.ws + S.o_enc);
+    auto* esc = reinterpret_cast<uint32_t*>(S.ws + S.o_esc);
+    auto* escsym = reinterpret_cast<uint16_t*>(S.ws + S.o_escsym);
+    MPS_CUDA_TRY(cudaMemsetAsync(decode_syms_i16, 0, (size_t)num_streams * TS * 2, st));
+    MPS_CUDA_TRY(cudaMemsetAsync(decode_nbits_u8, 0, (size_t)num_streams * TS, st));
+    MPS_CUDA_TRY(cudaMemsetAsync(stream_ctx, 0xFF, (size_t)num_streams * sizeof(int), st));
+    shared_rows_kernel<<<grid_for(S.G), 256, 0, st>>>(ctx_key, S.G, sid_lut_i32, row_of, stream_ctx);
+    for (long long g0 = 0; g0 < S.G; g0 += chunk) {
+        const long long g1 = (g0 + chunk < S.G) ? g0 + chunk : S.G;
+        codebook_kernel<<<(int)((g1 - g0 + 63) / 64), 64, 0, st>>>(items, counts, ctx_ofs, perm, g0, g1, L, S.variant, cs,
+                                                                    reinterpret_cast<uint16_t*>(decode_syms_i16),
+                                                                    decode_nbits_u8, enc, esc, escsym, S.d_flag, row_of);
+    }
+    MPS_CUDA_TRY(cudaGetLastError());
+    int flag = 0;
+    MPS_CUDA_TRY(cudaMemcpyAsync(&flag, S.d_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    if (flag == 2) { set_error("Internal error: not enough packages"); return (int)cudaErrorUnknown; }
+    return MPS_OK;
+}
+
+namespace {
+struct SharedArrays {   // what the layout call leaves in the workspace for the emit call
+    int* stream; uint32_t* lc; uint32_t* rel; int* chead; int* cidx;
+};
+SharedArrays shared_arrays(BuildState& S, Carver& C) {
+    SharedArrays a;
+    C.off = S.o_sh_end;
+    a.stream = C.take<int>(S.numel);
+    a.lc = C.take<uint32_t>(S.numel);
+    a.rel = C.take<uint32_t>(S.numel);
+    a.chead = C.take<int>(S.numel);
+    a.cidx = C.take<int>(S.numel);
+    return a;
+}
+}  // namespace
+
+int mps_build_shared_layout(mps_build_state* state, const uint16_t* bf16_bits, const uint8_t* int4_u8,
+                            const uint16_t* scales_u16, int32_t scale_mode, int64_t nb1, int64_t sb0, int64_t sb1,
+                            const int32_t* sid_lut_i32, int64_t* scale_bit_base_i64, void* stream,
+                            int64_t* num_chunks_out, int64_t* total_bits_out) {
+    if (!state || !bf16_bits || !int4_u8 || !scales_u16 || !sid_lut_i32 || !scale_bit_base_i64 || !num_chunks_out ||
+        !total_bits_out) {
+        set_error("mps_build_shared_layout: null argument");
+        return MPS_ERR_INVALID;
+    }
+    BuildState& S = *state_of(state);
+    if (S.variant != V_AWQ_SHARED || S.num_scales <= 0) { set_error("call mps_build_shared_codebooks first"); return MPS_ERR_INVALID; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long numel = S.numel, NS = S.num_scales;
+    Carver C{S.ws, 0, S.ws_bytes};
+    SharedArrays A = shared_arrays(S, C);
+    // scratch of this call
+    auto* nbits = C.take<int>(numel);
+    auto* tmp_a = C.take<int>(numel);      // run heads, then sorted scale ids
+    auto* tmp_b = C.take<int>(numel);      // run starts, then sorted element ids
+    auto* key = C.take<int>(numel);
+    auto* val = C.take<int>(numel);
+    auto* nb_sorted = C.take<int>(numel);
+    auto* cum = C.take<unsigned long long>(numel);
+    auto* seg_base = C.take<unsigned long long>(NS);
+    auto* seg_end = C.take<unsigned long long>(NS);
+    auto* d_res = C.take<long long>(4);
+    const size_t kCubTempBytes = cub_temp_bytes(numel);
+    void* cub_tmp = C.take<uint8_t>(kCubTempBytes);
+    if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
+    // kept by mps_build_shared_codebooks: row_of [G], then stream_ctx [num_streams]
+    auto* stream_ctx = reinterpret_cast<int*>(S.ws + align_up(S.o_sh_keep + (size_t)S.G * sizeof(int)));
+    CodeBook cb{reinterpret_cast<unsigned long long*>(S.ws + S.o_items), reinterpret_cast<int*>(S.ws + S.o_ctx_ofs),
+                reinterpret_cast<uint32_t*>(S.ws + S.o_enc), reinterpret_cast<uint32_t*>(S.ws + S.o_esc),
+                reinterpret_cast<uint16_t*>(S.ws + S.o_escsym)};
+    shared_elem_kernel<<<grid_for(numel), 256, 0, st>>>(bf16_bits, int4_u8, scales_u16, scale_mode, S.m, nb1, sb0, sb1,
+                                                        sid_lut_i32, stream_ctx, cb, numel, A.stream, A.lc, nbits, tmp_a,
+                                                        S.d_flag);
+    MPS_CUDA_TRY(cudaGetLastError());
+    size_t need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceScan::InclusiveScan(cub_tmp, need, tmp_a, tmp_b, cub::Max(), (int)numel, st));
+    shared_chunk_heads_kernel<<<grid_for(numel), 256, 0, st>>>(tmp_b, numel, A.chead);
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(cub_tmp, need, A.chead, A.cidx, (int)numel, st));
+    // every scale's elements in flat order: stable sort by scale id
+    shared_sid_keys_kernel<<<grid_for(numel), 256, 0, st>>>(A.stream, numel, key, val);
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceRadixSort::SortPairs(cub_tmp, need, key, tmp_a, val, tmp_b, (int)numel, 0, 16, st));
+    gather_i32_kernel<<<grid_for(numel), 256, 0, st>>>(nbits, tmp_b, numel, nb_sorted);
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceScan::InclusiveSum(cub_tmp, need, nb_sorted, cum, (int)numel, st));
+    MPS_CUDA_TRY(cudaMemsetAsync(seg_base, 0, (size_t)NS * 8, st));
+    MPS_CUDA_TRY(cudaMemsetAsync(seg_end, 0, (size_t)NS * 8, st));
+    shared_segments_kernel<<<grid_for(numel), 256, 0, st>>>(tmp_a, nb_sorted, cum, numel, seg_base, seg_end);
+    shared_relpos_kernel<<<grid_for(numel), 256, 0, st>>>(tmp_a, tmp_b, nb_sorted, cum, seg_base, numel, A.rel);
+    shared_bases_kernel<<<1, 32, 0, st>>>(seg_base, seg_end, NS, reinterpret_cast<long long*>(scale_bit_base_i64), d_res);
+    MPS_CUDA_TRY(cudaGetLastError());
+    long long total_bits = 0;
+    int last_head = 0, last_idx = 0, flag = 0;
+    MPS_CUDA_TRY(cudaMemcpyAsync(&total_bits, d_res, sizeof(long long), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaMemcpyAsync(&last_head, A.chead + (numel - 1), sizeof(int), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaMemcpyAsync(&last_idx, A.cidx + (numel - 1), sizeof(int), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaMemcpyAsync(&flag, S.d_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    if (flag == 3) { set_error("symbol not found in enc table for AWQ stream"); return (int)cudaErrorUnknown; }
+    S.num_chunks = (long long)last_idx + last_head;
+    *num_chunks_out = S.num_chunks;
+    *total_bits_out = total_bits;
+    return MPS_OK;
+}
+
+int mps_build_shared_emit(mps_build_state* state, const uint16_t* bf16_bits, const int64_t* scale_bit_base_i64,
+                          uint64_t* bitstream_u64, int64_t bitstream_words, uint32_t* chunk_startbit_rel_u32,
+                          uint32_t* chunk_out_base_u32, uint32_t* chunk_meta_u32, int32_t* chunk_scale_id_i32,
+                          int32_t* out_idx_i32, int64_t* stream_chunk_ofs_i64, int32_t* stream_chunk_ids_i32, void* stream) {
+    if (!state || !bf16_bits || !scale_bit_base_i64 || !bitstream_u64 || !chunk_startbit_rel_u32 || !chunk_out_base_u32 ||
+        !chunk_meta_u32 || !chunk_scale_id_i32 || !out_idx_i32 || !stream_chunk_ofs_i64 || !stream_chunk_ids_i32) {
+        set_error("mps_build_shared_emit: null argument");
+        return MPS_ERR_INVALID;
+    }
+    BuildState& S = *state_of(state);
+    if (S.variant != V_AWQ_SHARED || S.num_chunks <= 0) { set_error("call mps_build_shared_layout first"); return MPS_ERR_INVALID; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long long numel = S.numel, NC = S.num_chunks, num_streams = S.num_scales * 16;
+    Carver C{S.ws, 0, S.ws_bytes};
+    SharedArrays A = shared_arrays(S, C);
+    auto* cpos = C.take<int>(NC + 1);
+    auto* c_stream = C.take<int>(NC);
+    auto* c_stream_sorted = C.take<int>(NC);
+    auto* c_ids = C.take<int>(NC);
+    const size_t kCubTempBytes = cub_temp_bytes(numel);
+    void* cub_tmp = C.take<uint8_t>(kCubTempBytes);
+    if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
+    shared_chunk_pos_kernel<<<grid_for(numel), 256, 0, st>>>(A.chead, A.cidx, numel, NC, cpos);
+    shared_chunk_fill_kernel<<<grid_for(NC), 256, 0, st>>>(cpos, NC, A.stream, A.rel, chunk_startbit_rel_u32, chunk_out_base_u32,
+                                                           chunk_meta_u32, chunk_scale_id_i32, c_stream);
+    MPS_CUDA_TRY(cudaMemsetAsync(bitstream_u64, 0, (size_t)bitstream_words * 8, st));
+    shared_emit_kernel<<<grid_for(numel), 256, 0, st>>>(bf16_bits, A.stream, A.lc, A.rel,
+                                                        reinterpret_cast<const long long*>(scale_bit_base_i64), numel,
+                                                        reinterpret_cast<unsigned long long*>(bitstream_u64));
+    // chunk ids of every stream, ascending (stable sort by stream id) and the CSR offsets
+    iota_i32_kernel<<<grid_for(NC), 256, 0, st>>>(c_ids, NC);
+    size_t need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceRadixSort::SortPairs(cub_tmp, need, c_stream, c_stream_sorted, c_ids, stream_chunk_ids_i32, (int)NC,
+                                                 0, 21, st));
+    shared_stream_ofs_kernel<<<grid_for(num_streams + 1), 256, 0, st>>>(c_stream_sorted, NC, num_streams,
+                                                                        reinterpret_cast<long long*>(stream_chunk_ofs_i64));
+    iota_i32_kernel<<<grid_for(numel), 256, 0, st>>>(out_idx_i32, numel);
+    MPS_CUDA_TRY(cudaGetLastError());
+    MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    return MPS_OK;
+}
+
 
 }  // extern "C"

@@ -20,10 +20,6 @@ from . import _lib
 V_FP8, V_AWQ_BUCKET = 0, 1
 
 
-def _missing(name: str):
-    raise NotImplementedError(f"{name}: this sidecar layout has no GPU builder in this build of libmpserve_b200.so")
-
-
 def _device() -> torch.device:
     if not torch.cuda.is_available():
         raise RuntimeError("the sidecar builder needs a CUDA device (there is no CPU fallback)")
@@ -314,4 +310,78 @@ def build_awq_by_scale(bf16_values, int4_values, scales_u16, max_len, threads, g
 
 
 def build_awq_shared(bf16_params, int4_values_u8, scales_u16, max_len):
-    _missing("huffman_build_awq_decode_tables")
+    """huffman_build_awq_decode_tables (wrapper.cpp:182-209, build_huffman.cu:2157-2633): one table per
+    (scale id, int4 code) stream, one bitstream per scale, chunks of <= 255 same-stream elements."""
+    for t in (bf16_params, int4_values_u8, scales_u16):
+        if not isinstance(t, torch.Tensor):
+            raise ValueError("inputs must be defined")
+    if bf16_params.dtype != torch.bfloat16:
+        raise ValueError("bf16_params must be torch.bfloat16")
+    if int4_values_u8.dtype != torch.uint8:
+        raise ValueError("int4_values_u8 must be torch.uint8")
+    if scales_u16.dtype != torch.uint16:
+        raise ValueError("scales_u16 must be torch.uint16 (bf16 raw bits)")
+    if max_len <= 0 or max_len > 20:
+        raise ValueError("max_len must be in (0,20]")
+    if max_len > 15:
+        raise NotImplementedError("the GPU builder holds code lengths up to 15 bits")
+    if bf16_params.dim() != 2:
+        raise ValueError("bf16_params must be 2D [n,m]")
+    if tuple(int4_values_u8.shape) != tuple(bf16_params.shape):
+        raise ValueError("int4_values_u8 shape must match bf16_params")
+    lib = _lib.load()
+    dev = _device()
+    n, m = int(bf16_params.size(0)), int(bf16_params.size(1))
+    if n <= 0 or m <= 0:
+        raise ValueError("bf16_params shape must be non-empty")
+    s16 = scales_u16.contiguous()
+    mode, nb0, nb1, sb0, sb1 = _scale_mode(s16, n, m, False)
+    L = int(max_len)
+    numel = n * m
+    # dense ids of the scale values that occur, ascending by value (build_huffman.cu:2221-2256)
+    sv = np.unique(s16.cpu().numpy().reshape(-1))
+    S = int(sv.size)
+    lut = np.full(65536, -1, dtype=np.int32)
+    lut[sv] = np.arange(S, dtype=np.int32)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        sym_d = bf16_params.contiguous().view(torch.uint16).to(dev)
+        q_d = int4_values_u8.contiguous().to(dev)
+        sc_d = s16.to(dev)
+        lut_d = torch.from_numpy(lut).to(dev)
+        ws_bytes = int(lib.mps_build_workspace_bytes(numel, 8 * numel))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        state = (C.c_ubyte * 256)()
+        G, N = C.c_int64(0), C.c_int64(0)
+        _lib.check(lib.mps_build_analyze(state, sym_d.data_ptr(), q_d.data_ptr(), sc_d.data_ptr(), mode, nb1, sb0, sb1,
+                                         n, m, 3, L, ws.data_ptr(), ws_bytes, stream, C.byref(G), C.byref(N)))
+        TS = 1 << L
+        syms = torch.empty((S * 16, TS), dtype=torch.int16, device=dev)
+        nbits = torch.empty((S * 16, TS), dtype=torch.uint8, device=dev)
+        _lib.check(lib.mps_build_shared_codebooks(state, lut_d.data_ptr(), S, syms.data_ptr(), nbits.data_ptr(), stream))
+        sbase = torch.empty((S + 1,), dtype=torch.int64, device=dev)
+        nchunks, total_bits = C.c_int64(0), C.c_int64(0)
+        _lib.check(lib.mps_build_shared_layout(state, sym_d.data_ptr(), q_d.data_ptr(), sc_d.data_ptr(), mode, nb1, sb0,
+                                               sb1, lut_d.data_ptr(), sbase.data_ptr(), stream, C.byref(nchunks),
+                                               C.byref(total_bits)))
+        NC, words = int(nchunks.value), int(total_bits.value) >> 6
+        bits = torch.empty((words,), dtype=torch.uint64, device=dev)
+        c_start = torch.empty((NC,), dtype=torch.uint32, device=dev)
+        c_base = torch.empty((NC,), dtype=torch.uint32, device=dev)
+        c_meta = torch.empty((NC,), dtype=torch.uint32, device=dev)
+        c_sid = torch.empty((NC,), dtype=torch.int32, device=dev)
+        out_idx = torch.empty((numel,), dtype=torch.int32, device=dev)
+        s_ofs = torch.empty((S * 16 + 1,), dtype=torch.int64, device=dev)
+        s_ids = torch.empty((NC,), dtype=torch.int32, device=dev)
+        _lib.check(lib.mps_build_shared_emit(state, sym_d.data_ptr(), sbase.data_ptr(), bits.data_ptr(), words,
+                                             c_start.data_ptr(), c_base.data_ptr(), c_meta.data_ptr(), c_sid.data_ptr(),
+                                             out_idx.data_ptr(), s_ofs.data_ptr(), s_ids.data_ptr(), stream))
+        out = {
+            "decode_syms_i16": syms, "decode_nbits_u8": nbits, "scale_values_u16": torch.from_numpy(sv.astype(np.uint16)),
+            "scale_bit_base_i64": sbase, "chunk_startbit_rel_u32": c_start, "chunk_out_base_u32": c_base,
+            "chunk_meta_u32": c_meta, "chunk_scale_id_i32": c_sid, "out_idx_i32": out_idx,
+            "stream_chunk_ofs_i64": s_ofs, "stream_chunk_ids_i32": s_ids, "bitstream_u64": bits,
+        }
+        torch.cuda.synchronize(dev)
+        keep_on_device = bf16_params.is_cuda
+        return {k_: (v if keep_on_device and v.is_cuda else v.cpu()) for k_, v in out.items()}

@@ -118,6 +118,51 @@ def test_awq_by_scale_builder_matches_oracle(scale_kind, L, cap):
     _same(got, want, f"{scale_kind} L={L}")
 
 
+@pytest.mark.parametrize("name", [n for n in golden_names("awq") if n.endswith("_shared")])
+def test_awq_shared_builder_matches_reference_golden(golden_cases, name):
+    import MPServe_cuda
+
+    g = golden_cases[name]
+    got = MPServe_cuda.huffman_build_awq_decode_tables(
+        torch.from_numpy(g.bf16).view(torch.bfloat16), torch.from_numpy(g.ctx), torch.from_numpy(g.scales),
+        max_len=g.params["max_len"])
+    g.check_artifacts({k: _np(v) for k, v in got.items()})
+
+
+@pytest.mark.parametrize("scale_kind,L,dist", [("group", 11, "normal"), ("row", 11, "normal"), ("scalar", 11, "normal"),
+                                                ("scalar", 6, "student_t"), ("row", 8, "student_t"),
+                                                ("group", 9, "student_t")])
+def test_awq_shared_builder_matches_oracle(scale_kind, L, dist):
+    import MPServe_cuda
+
+    n, m = 128, 512
+    c = wl.quantize_awq(wl.random_weight(n, m, 57, dist), 128)
+    sc = c.scales_u16
+    if scale_kind == "row":
+        sc = sc[:, 0].contiguous()
+    elif scale_kind == "scalar":
+        sc = sc[:1, 0].contiguous().reshape(1)
+    want = orc.build_awq_shared(c.bf16.view(torch.uint16).numpy(), c.int4_u8.numpy(), sc.numpy(), L)
+    got = MPServe_cuda.huffman_build_awq_decode_tables(c.bf16, c.int4_u8, sc, max_len=L)
+    _same(got, want, f"{scale_kind} L={L}")
+
+
+def test_awq_shared_build_then_decode_on_device():
+    import MPServe_cuda
+
+    dev = torch.device("cuda:0")
+    n, m = 256, 1024
+    c = wl.quantize_awq(wl.random_weight(n, m, 58, "normal"), 128)
+    d = MPServe_cuda.huffman_build_awq_decode_tables(c.bf16.to(dev), c.int4_u8.to(dev), c.scales_u16.to(dev), max_len=11)
+    assert all(v.is_cuda for k, v in d.items() if k != "scale_values_u16")
+    out = MPServe_cuda.huffman_decode_awq_shared_table(
+        d["bitstream_u64"], d["decode_syms_i16"], d["decode_nbits_u8"], d["scale_bit_base_i64"],
+        d["chunk_startbit_rel_u32"], d["chunk_out_base_u32"], d["chunk_meta_u32"], d["chunk_scale_id_i32"],
+        d["out_idx_i32"], d["stream_chunk_ofs_i64"], d["stream_chunk_ids_i32"], n * m, 11)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.uint16).reshape(n, m).cpu(), c.bf16.view(torch.uint16))
+
+
 def test_build_then_decode_roundtrip_on_device():
     """Encoder output fed straight to the decoder, everything resident on the GPU."""
     import MPServe_cuda
