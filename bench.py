@@ -218,21 +218,42 @@ def run_ours(args, rank, world, local_rank):
     log(f"[rank {rank}] generated, quantised and encoded {layers} layers ({n_elem / 1e9:.2f} G elements) on the GPU "
         f"in {enc_s:.1f}s")
 
-    # pinned host copies of every compressed input (what a loader would hold), for the end-to-end leg
-    entries, copies = [], []
+    # Every layer's compressed inputs are packed into one device buffer with a pinned host twin (what a
+    # loader would hold), so the end-to-end leg moves a layer with one copy; the tensors the decoder
+    # reads are views into the device buffer.
+    entries, layer_entries, layer_bufs = [], [], []
     alg_bytes = 0
     for layer in model:
+        arrays = []
         for name, n, m, c, art in layer:
-            d = {k: art[k] for k in DECODE_KEYS}
-            copies.append((c.fp8_u8, c.fp8_u8.cpu().pin_memory()))
-            copies.extend((d[k], d[k].cpu().pin_memory()) for k in DECODE_KEYS)
-            entries.append((c.fp8_u8, d, None))
+            arrays.append(c.fp8_u8)
+            arrays.extend(art[k] for k in DECODE_KEYS)
+        offs, total = [], 0
+        for a in arrays:
+            offs.append(total)
+            total += (a.numel() * a.element_size() + 255) // 256 * 256
+        flat = torch.empty(total, dtype=torch.uint8, device=dev)
+        views = []
+        for a, o in zip(arrays, offs):
+            v = flat[o:o + a.numel() * a.element_size()].view(a.dtype).view(a.shape)
+            v.copy_(a)
+            views.append(v)
+        it = iter(views)
+        these = []
+        for item in layer:
+            name, n, m, c, art = item
+            c.fp8_u8 = next(it)
+            d = {k: next(it) for k in DECODE_KEYS}
+            for k in DECODE_KEYS:
+                art[k] = d[k]
+            these.append((c.fp8_u8, d, None))
             alg_bytes += n * m + sum(v.numel() * v.element_size() for v in d.values()) + 2 * n * m
-    h2d_bytes = sum(s.numel() * s.element_size() for _, s in copies)
-
-    def upload():
-        for dst, src in copies:
-            dst.copy_(src, non_blocking=True)
+        entries.extend(these)
+        layer_entries.append(these)
+        layer_bufs.append((flat, flat.cpu().pin_memory()))
+        del arrays, views
+    torch.cuda.empty_cache()
+    h2d_bytes = sum(f.numel() for f, _ in layer_bufs)
 
     plan = api.BucketDecodePlan(entries, mode=0)
     out_bytes = sum(o.numel() * 2 for o in plan.outputs)
@@ -306,20 +327,40 @@ def run_ours(args, rank, world, local_rank):
     ms_per_step = total_ms / args.steps
 
     # ---- end to end: pinned host -> device copy of the compressed inputs, decode, checksum back ------
+    # One plan per layer over the same buffers and outputs: layer i is decoded (and check-summed) on the
+    # compute stream while layer i+1 crosses PCIe on the copy stream.
+    idx = 0
+    layer_plans = []
+    for these in layer_entries:
+        with_out = [(ctx, d, plan.outputs[idx + j]) for j, (ctx, d, _) in enumerate(these)]
+        layer_plans.append(api.BucketDecodePlan(with_out, mode=0))
+        idx += len(these)
+    copy_stream = torch.cuda.Stream(device=dev)
+    main_stream = torch.cuda.current_stream(dev)
     acc = torch.zeros(2, dtype=torch.int64, device=dev)
     e2e_steps = max(1, min(args.steps, 3))
-    upload(); plan.decode(); torch.cuda.synchronize()
+
+    def e2e_step():
+        acc.zero_()
+        copy_stream.wait_stream(main_stream)   # the previous step's decodes have read the buffers
+        for (flat_dev, flat_host), lp in zip(layer_bufs, layer_plans):
+            with torch.cuda.stream(copy_stream):
+                flat_dev.copy_(flat_host, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_stream)
+            main_stream.wait_event(ev)
+            for o in lp.decode():
+                api.checksum_u16(o, acc)
+        return acc.cpu()
+
+    e2e_step()
+    torch.cuda.synchronize()
     barrier()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
-        upload()
-        plan.decode()
-        acc.zero_()
-        for o in plan.outputs:
-            api.checksum_u16(o, acc)
-        acc_host = acc.cpu()
+        acc_host = e2e_step()
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
@@ -327,6 +368,7 @@ def run_ours(args, rank, world, local_rank):
     if use_dist:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t[0])
+    e2e_launches = e2e_steps * (len(layer_plans) + len(entries))
 
     # ---- checksum of all ranks' outputs over NCCL (outside every timed region) -------------------------
     got_sum = int(acc_host[0]) % (1 << 64)
@@ -378,7 +420,9 @@ def run_ours(args, rank, world, local_rank):
                      "kernel_ms": kernel_ms_max},
         "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 16,
-                "ms_per_step": e2e_ms},
+                "ms_per_step": e2e_ms, "steps": e2e_steps, "gpu_launches": e2e_launches,
+                "how": "per layer: one pinned-host -> device copy of its packed compressed inputs on a copy stream, "
+                       "then one decode launch and the checksums on the compute stream; 16 bytes read back per step"},
         "gpu_launches": args.steps,
         "clocks": clocks,
     }

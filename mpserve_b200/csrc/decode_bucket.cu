@@ -356,21 +356,16 @@ __device__ __forceinline__ void decode_vec(const Smem& sm, const uint32_t* rowba
 // wants tens of KB in flight per SM; register prefetch gave a few KB).
 //
 //  * Context bytes: a dedicated producer warp issues cp.async.bulk (the TMA bulk-copy engine, no tensor
-//    map, no multicast) of the SPAN contiguous bytes every step needs, kSteps steps per stage,
-//    kStages stages ahead; stages are handed over with full/empty mbarriers.  Consumers read their
-//    CH bytes of a step with one conflict-free shared-memory load.
-//  * Bitstream: each sub-stream owns 32 bytes of shared memory (two 16-byte halves).  When its
-//    window moves into a 16-byte chunk it starts the cp.async of the following chunk into the half
-//    it just left; groups are committed once per block by every thread and awaited with
-//    cp.async.wait_group kBitLag, i.e. a copy has kBitLag whole blocks to land.  A chunk holds at
-//    least five blocks' worth of bits (a block consumes < 32 bits), so kBitLag = 4 is always safe.
-//    The divergent access (every lane a different 128-byte line) thus happens once per 16 bytes
-//    (~32 symbols) per sub-stream instead of once per 4 bytes.
+//    map, no multicast) of the SPAN contiguous bytes every step needs, kSS steps per stage, several
+//    stages ahead; stages are handed over with full/empty mbarriers.  Consumers read their CH bytes
+//    of a step with one conflict-free shared-memory load.
+//  * Bitstream: each sub-stream owns a ring of kRingChunks 16-byte chunks in shared memory and keeps
+//    the chunks ahead of its window requested with cp.async: at most one new request every CHK steps,
+//    committed as a group by every thread and awaited with cp.async.wait_group LAG, where LAG follows
+//    from the most bits CHK steps can consume (see stream_run).  The divergent access (every lane a
+//    different 128-byte line) thus happens once per 16 bytes (~21 symbols) per sub-stream instead of
+//    once per 4 bytes.
 // ------------------------------------------------------------------------------------------------
-#ifndef MPS_BITLAG
-#define MPS_BITLAG 4
-#endif
-constexpr int kBitLag = MPS_BITLAG;
 constexpr uint32_t kSpinLimit = 1u << 22;  // bounded waits: give up, flag, return
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

@@ -2,7 +2,7 @@
 
     python -m mpserve_b200.sweep single          # one 4096x4096 weight, per-tensor FP8 scale
     python -m mpserve_b200.sweep sizes           # 64 KB ... 1 GB of BF16 output, N(0,0.02) and Student-t(4)
-    python -m mpserve_b200.sweep awq             # Llama-3-8B-shaped linears as INT4 (group 128), both bucket layouts
+    python -m mpserve_b200.sweep awq             # Llama-3-8B-shaped linears as INT4 (group 128), the three sidecar layouts
 
 Every case is generated, quantised and encoded on the GPU by this library's own builder, decoded
 through the per-tensor entry point the reference's plugin calls (``huffman_decode_fp8`` and the AWQ
@@ -49,6 +49,9 @@ def _art_bytes(art: dict, keys) -> int:
 _FP8_KEYS = ("bitstream_u64", "decode_syms_u16", "decode_lens_u8", "bucket_table_i32", "bucket_col_start_i32",
              "bucket_col_len_i32", "bucket_row_offsets_i32", "row_indices_i32", "bucket_thread_startbit_u32",
              "bucket_bit_base_i64")
+_SHARED_KEYS = ("bitstream_u64", "decode_syms_i16", "decode_nbits_u8", "scale_bit_base_i64", "chunk_startbit_rel_u32",
+                "chunk_out_base_u32", "chunk_meta_u32", "chunk_scale_id_i32", "out_idx_i32", "stream_chunk_ofs_i64",
+                "stream_chunk_ids_i32")
 _BYSCALE_KEYS = ("bitstream_u64", "decode_syms_u16", "decode_lens_u8", "bucket_table_i32", "bucket_group_offsets_i32",
                  "group_rows_i32", "group_col_start_i32", "bucket_thread_startbit_u32", "bucket_bit_base_i64")
 
@@ -90,6 +93,13 @@ def awq_case(name: str, n: int, m: int, layout: str, k: int, seed: int, dev, flu
 
         def run():
             return MPServe_cuda.huffman_decode_awq_int4_bucket(c.int4_u8, *a, n, m, 11)
+    elif layout == "shared":
+        art = MPServe_cuda.huffman_build_awq_decode_tables(c.bf16, c.int4_u8, c.scales_u16, max_len=11)
+        keys = _SHARED_KEYS
+        a = [art[key] for key in keys]
+
+        def run():
+            return MPServe_cuda.huffman_decode_awq_shared_table(*a, n * m, 11).view(torch.bfloat16).view(n, m)
     else:
         art = MPServe_cuda.huffman_build_awq_int4_bucket_decode_tables_by_scale(c.bf16, c.int4_u8, c.scales_u16, max_len=11,
                                                                                 threads=k, group_cap=1024)
@@ -105,12 +115,13 @@ def awq_case(name: str, n: int, m: int, layout: str, k: int, seed: int, dev, flu
     assert torch.equal(out.view(torch.uint16), c.bf16.view(torch.uint16)), "decode mismatch"
     med, best = _time_calls(run, flush, reps)
     elems = n * m
-    alg = elems + _art_bytes(art, keys) + 2 * elems
+    alg = (0 if layout == "shared" else elems) + _art_bytes(art, keys) + 2 * elems   # the shared layout reads no int4 codes
     return {"case": f"awq g128 {layout} {name} {n}x{m} k={k}", "out_bytes": 2 * elems, "ms_median": med, "ms_best": best,
             "bf16_gbps": 2 * elems / med / 1e6, "algorithmic_gbps": alg / med / 1e6,
             "algorithmic_bytes_per_element": alg / elems,
             "code_bits_per_element": 64.0 * art["bitstream_u64"].numel() / elems,
-            "buckets": int(art["bucket_table_i32"].size(0)), "tables": int(art["decode_syms_u16"].size(0))}
+            "buckets": int(art["bucket_table_i32"].size(0)) if layout != "shared" else int(art["chunk_meta_u32"].numel()),
+            "tables": int(art["decode_syms_u16" if layout != "shared" else "decode_syms_i16"].size(0))}
 
 
 SIZES = [(128, 256), (256, 512), (512, 1024), (1024, 2048), (2048, 4096), (4096, 4096), (8192, 8192), (16384, 8192),
@@ -145,8 +156,10 @@ def main(argv=None) -> int:
                 torch.cuda.empty_cache()
     else:
         k = args.k or 256
-        for layout in ("byscale", "bucket"):
+        for layout in ("byscale", "bucket", "shared"):
             for i, (name, n, m) in enumerate(wl.layer_linears(wl.LLAMA3_8B)):
+                if layout == "shared" and i not in (0, 1):
+                    continue   # one square and one small tensor: the format's metadata is ~20 B per element
                 rows.append(awq_case(name, n, m, layout, k, 100 + i, dev, flush, max(3, args.reps // 3)))
                 print(json.dumps(rows[-1]), flush=True)
                 torch.cuda.empty_cache()
