@@ -526,13 +526,13 @@ __global__ void table_keys_kernel(const uint32_t* __restrict__ ctx_key, long lon
 // ------------------------------------------------------------------------------------------------
 __global__ void shared_rows_kernel(const uint32_t* __restrict__ ctx_key, long long G, const int32_t* __restrict__ sid_lut,
                                    int* __restrict__ row_of, int* __restrict__ stream_ctx) {
-    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (g >= G) return;
-    const uint32_t key = ctx_key[g];
-    const int sid = sid_lut[key >> 16];
-    const int row = sid * 16 + (int)(key & 0xFu);
-    row_of[g] = row;
-    stream_ctx[row] = (int)g;
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < G; g += (long long)gridDim.x * blockDim.x) {
+        const uint32_t key = ctx_key[g];
+        const int sid = sid_lut[key >> 16];
+        const int row = sid * 16 + (int)(key & 0xFu);
+        row_of[g] = row;
+        stream_ctx[row] = (int)g;
+    }
 }
 
 // per element: its stream, its code (len << 16 | code, bit 31: 16 raw bits follow) and its bit count
@@ -542,61 +542,62 @@ __global__ void shared_elem_kernel(const uint16_t* __restrict__ sym, const uint8
                                    const int* __restrict__ stream_ctx, CodeBook cb, long long numel,
                                    int* __restrict__ stream, uint32_t* __restrict__ lc, int* __restrict__ nbits,
                                    int* __restrict__ run_head, int* __restrict__ err) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= numel) return;
-    auto stream_at = [&](long long e) -> int {
-        uint16_t sc;
-        if (scale_mode == 0) sc = scales[0];
-        else {
-            const long long r = e / m, c = e - r * m;
-            sc = (scale_mode == 1) ? scales[r] : scales[(r / sb0) * nb1 + (c / sb1)];
-        }
-        return sid_lut[sc] * 16 + (int)(q[e] & 0xFu);
-    };
-    const int st = stream_at(i);
-    stream[i] = st;
-    run_head[i] = (i == 0 || stream_at(i - 1) != st) ? (int)i : 0;
-    const int gid = stream_ctx[st];
-    uint32_t code = 0; int len = 0; bool raw = false;
-    const int nb = (gid >= 0) ? element_code(cb, gid, sym[i], code, len, raw) : -1;
-    if (nb < 0) { atomicExch(err, 3); lc[i] = 0; nbits[i] = 0; return; }
-    lc[i] = ((uint32_t)len << 16) | code | (raw ? 0x80000000u : 0u);
-    nbits[i] = nb;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += (long long)gridDim.x * blockDim.x) {
+        auto stream_at = [&](long long e) -> int {
+            uint16_t sc;
+            if (scale_mode == 0) sc = scales[0];
+            else {
+                const long long r = e / m, c = e - r * m;
+                sc = (scale_mode == 1) ? scales[r] : scales[(r / sb0) * nb1 + (c / sb1)];
+            }
+            return sid_lut[sc] * 16 + (int)(q[e] & 0xFu);
+        };
+        const int st = stream_at(i);
+        stream[i] = st;
+        run_head[i] = (i == 0 || stream_at(i - 1) != st) ? (int)i : 0;
+        const int gid = stream_ctx[st];
+        uint32_t code = 0; int len = 0; bool raw = false;
+        const int nb = (gid >= 0) ? element_code(cb, gid, sym[i], code, len, raw) : -1;
+        if (nb < 0) { atomicExch(err, 3); lc[i] = 0; nbits[i] = 0; continue; }
+        lc[i] = ((uint32_t)len << 16) | code | (raw ? 0x80000000u : 0u);
+        nbits[i] = nb;
+    }
 }
 
 __global__ void shared_chunk_heads_kernel(const int* __restrict__ run_start, long long numel, int* __restrict__ chead) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < numel) chead[i] = ((i - run_start[i]) % 255 == 0) ? 1 : 0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += (long long)gridDim.x * blockDim.x)
+        chead[i] = ((i - run_start[i]) % 255 == 0) ? 1 : 0;
 }
 
 __global__ void shared_sid_keys_kernel(const int* __restrict__ stream, long long numel, int* __restrict__ key, int* __restrict__ val) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < numel) { key[i] = stream[i] >> 4; val[i] = (int)i; }
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += (long long)gridDim.x * blockDim.x)
+        { key[i] = stream[i] >> 4; val[i] = (int)i; }
 }
 
-__global__ void gather_i32_kernel(const int* __restrict__ src, const int* __restrict__ idx, long long N, int* __restrict__ dst) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < N) dst[i] = src[idx[i]];
+__global__ void gather_bits_kernel(const int* __restrict__ src, const int* __restrict__ idx, long long N,
+                                   unsigned long long* __restrict__ dst) {   // 64-bit: the running sum passes 2^31 bits
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < N; i += (long long)gridDim.x * blockDim.x)
+        dst[i] = (unsigned long long)src[idx[i]];
 }
 
 // in scale-sorted order: where every scale's run starts and how many bits it holds
-__global__ void shared_segments_kernel(const int* __restrict__ sid_sorted, const int* __restrict__ nb_sorted,
+__global__ void shared_segments_kernel(const int* __restrict__ sid_sorted, const unsigned long long* __restrict__ nb_sorted,
                                        const unsigned long long* __restrict__ cum, long long numel,
                                        unsigned long long* __restrict__ seg_base, unsigned long long* __restrict__ seg_bits_end) {
-    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= numel) return;
-    const int sid = sid_sorted[j];
-    if (j == 0 || sid_sorted[j - 1] != sid) seg_base[sid] = cum[j] - (unsigned long long)nb_sorted[j];
-    if (j == numel - 1 || sid_sorted[j + 1] != sid) seg_bits_end[sid] = cum[j];
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < numel; j += (long long)gridDim.x * blockDim.x) {
+        const int sid = sid_sorted[j];
+        if (j == 0 || sid_sorted[j - 1] != sid) seg_base[sid] = cum[j] - nb_sorted[j];
+        if (j == numel - 1 || sid_sorted[j + 1] != sid) seg_bits_end[sid] = cum[j];
+    }
 }
 
 __global__ void shared_relpos_kernel(const int* __restrict__ sid_sorted, const int* __restrict__ idx_sorted,
-                                     const int* __restrict__ nb_sorted, const unsigned long long* __restrict__ cum,
+                                     const unsigned long long* __restrict__ nb_sorted, const unsigned long long* __restrict__ cum,
                                      const unsigned long long* __restrict__ seg_base, long long numel,
                                      uint32_t* __restrict__ rel) {
-    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= numel) return;
-    rel[idx_sorted[j]] = (uint32_t)(cum[j] - (unsigned long long)nb_sorted[j] - seg_base[sid_sorted[j]]);
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < numel; j += (long long)gridDim.x * blockDim.x) {
+        rel[idx_sorted[j]] = (uint32_t)(cum[j] - nb_sorted[j] - seg_base[sid_sorted[j]]);
+    }
 }
 
 // scale_bit_base: every scale's bitstream starts on a 64-bit boundary (:2543-2560); res[0] = total bits
@@ -616,65 +617,66 @@ __global__ void shared_bases_kernel(const unsigned long long* __restrict__ seg_b
 
 __global__ void shared_chunk_pos_kernel(const int* __restrict__ chead, const int* __restrict__ cidx, long long numel,
                                         long long C, int* __restrict__ cpos) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < numel && chead[i]) cpos[cidx[i]] = (int)i;
-    if (i == 0) cpos[C] = (int)numel;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += (long long)gridDim.x * blockDim.x) {
+        if (chead[i]) cpos[cidx[i]] = (int)i;
+        if (i == 0) cpos[C] = (int)numel;
+    }
 }
 
 __global__ void shared_chunk_fill_kernel(const int* __restrict__ cpos, long long C, const int* __restrict__ stream,
                                          const uint32_t* __restrict__ rel, uint32_t* __restrict__ c_start,
                                          uint32_t* __restrict__ c_base, uint32_t* __restrict__ c_meta,
                                          int32_t* __restrict__ c_sid, int* __restrict__ c_stream) {
-    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    const int i = cpos[c];
-    const int st = stream[i];
-    c_base[c] = (uint32_t)i;
-    c_start[c] = rel[i];
-    c_sid[c] = st >> 4;
-    c_meta[c] = ((uint32_t)(cpos[c + 1] - i) << 8) | (uint32_t)(st & 15);
-    c_stream[c] = st;
+    for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < C; c += (long long)gridDim.x * blockDim.x) {
+        const int i = cpos[c];
+        const int st = stream[i];
+        c_base[c] = (uint32_t)i;
+        c_start[c] = rel[i];
+        c_sid[c] = st >> 4;
+        c_meta[c] = ((uint32_t)(cpos[c + 1] - i) << 8) | (uint32_t)(st & 15);
+        c_stream[c] = st;
+    }
 }
 
 __global__ void shared_emit_kernel(const uint16_t* __restrict__ sym, const int* __restrict__ stream,
                                    const uint32_t* __restrict__ lc, const uint32_t* __restrict__ rel,
                                    const long long* __restrict__ scale_bit_base, long long numel,
                                    unsigned long long* __restrict__ bitstream) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= numel) return;
-    const uint32_t v = lc[i];
-    const int len = (int)((v >> 16) & 0x7FFFu);
-    const bool raw = (v >> 31) != 0;
-    unsigned long long bits = v & 0xFFFFu;
-    int nb = len;
-    if (raw) { bits = (bits << 16) | sym[i]; nb += 16; }
-    if (nb <= 0) return;
-    const long long pos = scale_bit_base[stream[i] >> 4] + (long long)rel[i];
-    const long long w = pos >> 6;
-    const int o = (int)(pos & 63);
-    if (o + nb <= 64) atomicOr(&bitstream[w], bits << (64 - o - nb));
-    else {
-        const int second = o + nb - 64;
-        atomicOr(&bitstream[w], bits >> second);
-        atomicOr(&bitstream[w + 1], bits << (64 - second));
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += (long long)gridDim.x * blockDim.x) {
+        const uint32_t v = lc[i];
+        const int len = (int)((v >> 16) & 0x7FFFu);
+        const bool raw = (v >> 31) != 0;
+        unsigned long long bits = v & 0xFFFFu;
+        int nb = len;
+        if (raw) { bits = (bits << 16) | sym[i]; nb += 16; }
+        if (nb <= 0) continue;
+        const long long pos = scale_bit_base[stream[i] >> 4] + (long long)rel[i];
+        const long long w = pos >> 6;
+        const int o = (int)(pos & 63);
+        if (o + nb <= 64) atomicOr(&bitstream[w], bits << (64 - o - nb));
+        else {
+            const int second = o + nb - 64;
+            atomicOr(&bitstream[w], bits >> second);
+            atomicOr(&bitstream[w + 1], bits << (64 - second));
+        }
     }
 }
 
 __global__ void shared_stream_ofs_kernel(const int* __restrict__ keys_sorted, long long C, long long num_streams,
                                          long long* __restrict__ ofs) {
-    const long long s = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (s > num_streams) return;
-    long long lo = 0, hi = C;  // first chunk whose stream is >= s
-    while (lo < hi) {
-        const long long mid = (lo + hi) >> 1;
-        if (keys_sorted[mid] < s) lo = mid + 1; else hi = mid;
+    for (long long s = (long long)blockIdx.x * blockDim.x + threadIdx.x; s <= num_streams; s += (long long)gridDim.x * blockDim.x) {
+        long long lo = 0, hi = C;  // first chunk whose stream is >= s
+        while (lo < hi) {
+            const long long mid = (lo + hi) >> 1;
+            if (keys_sorted[mid] < s) lo = mid + 1; else hi = mid;
+        }
+        ofs[s] = lo;
     }
-    ofs[s] = lo;
 }
 
 __global__ void iota_i32_kernel(int32_t* __restrict__ p, long long n) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) p[i] = (int32_t)i;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        p[i] = (int32_t)i;
 }
 
 }  // namespace mps
@@ -1072,7 +1074,7 @@ int mps_build_shared_layout(mps_build_state* state, const uint16_t* bf16_bits, c
     auto* tmp_b = C.take<int>(numel);      // run starts, then sorted element ids
     auto* key = C.take<int>(numel);
     auto* val = C.take<int>(numel);
-    auto* nb_sorted = C.take<int>(numel);
+    auto* nb_sorted = C.take<unsigned long long>(numel);
     auto* cum = C.take<unsigned long long>(numel);
     auto* seg_base = C.take<unsigned long long>(NS);
     auto* seg_end = C.take<unsigned long long>(NS);
@@ -1098,7 +1100,7 @@ int mps_build_shared_layout(mps_build_state* state, const uint16_t* bf16_bits, c
     shared_sid_keys_kernel<<<grid_for(numel), 256, 0, st>>>(A.stream, numel, key, val);
     need = kCubTempBytes;
     MPS_CUDA_TRY(cub::DeviceRadixSort::SortPairs(cub_tmp, need, key, tmp_a, val, tmp_b, (int)numel, 0, 16, st));
-    gather_i32_kernel<<<grid_for(numel), 256, 0, st>>>(nbits, tmp_b, numel, nb_sorted);
+    gather_bits_kernel<<<grid_for(numel), 256, 0, st>>>(nbits, tmp_b, numel, nb_sorted);
     need = kCubTempBytes;
     MPS_CUDA_TRY(cub::DeviceScan::InclusiveSum(cub_tmp, need, nb_sorted, cum, (int)numel, st));
     MPS_CUDA_TRY(cudaMemsetAsync(seg_base, 0, (size_t)NS * 8, st));
@@ -1127,7 +1129,11 @@ int mps_build_shared_emit(mps_build_state* state, const uint16_t* bf16_bits, con
                           int32_t* out_idx_i32, int64_t* stream_chunk_ofs_i64, int32_t* stream_chunk_ids_i32, void* stream) {
     if (!state || !bf16_bits || !scale_bit_base_i64 || !bitstream_u64 || !chunk_startbit_rel_u32 || !chunk_out_base_u32 ||
         !chunk_meta_u32 || !chunk_scale_id_i32 || !out_idx_i32 || !stream_chunk_ofs_i64 || !stream_chunk_ids_i32) {
-        set_error("mps_build_shared_emit: null argument");
+        set_error("mps_build_shared_emit: null argument (state %d, inputs %d%d, bitstream %d, chunks %d%d%d%d, out_idx %d, csr %d%d)",
+                  state != nullptr, bf16_bits != nullptr, scale_bit_base_i64 != nullptr, bitstream_u64 != nullptr,
+                  chunk_startbit_rel_u32 != nullptr, chunk_out_base_u32 != nullptr, chunk_meta_u32 != nullptr,
+                  chunk_scale_id_i32 != nullptr, out_idx_i32 != nullptr, stream_chunk_ofs_i64 != nullptr,
+                  stream_chunk_ids_i32 != nullptr);
         return MPS_ERR_INVALID;
     }
     BuildState& S = *state_of(state);

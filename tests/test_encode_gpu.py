@@ -147,11 +147,11 @@ def test_awq_shared_builder_matches_oracle(scale_kind, L, dist):
     _same(got, want, f"{scale_kind} L={L}")
 
 
-def test_awq_shared_build_then_decode_on_device():
+@pytest.mark.parametrize("n,m", [(256, 1024), (2048, 4096)])   # the larger one spans many grid strides
+def test_awq_shared_build_then_decode_on_device(n, m):
     import MPServe_cuda
 
     dev = torch.device("cuda:0")
-    n, m = 256, 1024
     c = wl.quantize_awq(wl.random_weight(n, m, 58, "normal"), 128)
     d = MPServe_cuda.huffman_build_awq_decode_tables(c.bf16.to(dev), c.int4_u8.to(dev), c.scales_u16.to(dev), max_len=11)
     assert all(v.is_cuda for k, v in d.items() if k != "scale_values_u16")
