@@ -1235,12 +1235,13 @@ static int env_int(const char* name, int dflt) {
 }
 
 // threads x chains = sub-streams per work item.  Wide items (more chains per thread) cost fewer
-// instructions per symbol; narrow items give more CTAs something to do when a launch has few
-// sub-streams in total.
+// instructions per symbol and keep an SM 2.6 times busier than one chain per thread does; narrow
+// items give more SMs something to do when a launch has few sub-streams in total.  Halving the width
+// pays only while the wider shape would leave more than half of the SMs idle.
 static void pick_config(long long total_substreams, int k_min, int* threads, int* chains) {
     const int sms = sm_count();
     int t = 256, c = 4;
-    while (c > 1 && (t * c > k_min || total_substreams / ((long long)t * c) < 2LL * sms)) c >>= 1;
+    while (c > 1 && (t * c > k_min || 2 * (total_substreams / ((long long)t * c)) <= sms)) c >>= 1;
     while (t > 256 && t * c > k_min) t >>= 1;
     const int et = env_int("MPS_DECODE_THREADS", 0), ec = env_int("MPS_DECODE_CHAINS", 0);
     if (et > 0) t = et;
