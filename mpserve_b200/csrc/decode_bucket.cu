@@ -52,11 +52,16 @@ int cuda_fail(cudaError_t e, const char* what) {
 // ------------------------------------------------------------------------------------------------
 constexpr int kTableEntries = 32768;  // 256 ctx x 2^7 == 16 ctx x 2^11
 constexpr int kRowCap = 1024;         // rows / groups of a bucket cached in shared memory
-constexpr int kPrefixCap = 16;        // tensors of a batch whose item prefix is cached in shared memory
 constexpr int kSteps = 4;             // steps per software-pipeline block (register-prefetch path)
 constexpr int kSS = 8;                // steps per stage of the streaming path's context ring
 #ifndef MPS_LOOK
 #define MPS_LOOK 1
+#endif
+#ifndef MPS_UNCHECKED
+#define MPS_UNCHECKED 1
+#endif
+#ifndef MPS_STEPOFS
+#define MPS_STEPOFS 1
 #endif
 #ifndef MPS_COOP_BEGIN
 #define MPS_COOP_BEGIN 1
@@ -78,7 +83,8 @@ struct BatchArgs {
 #define MPS_STAGES 3
 #endif
 constexpr int kStages = MPS_STAGES;            // context-byte ring: stages of kSS steps each for the widest items
-constexpr int kMaxStages = 4 * kStages;        // narrower items split the same ring into more stages
+constexpr int kMaxStages = 8;                  // narrower items split the same ring into more stages
+static_assert(kMaxStages >= kStages, "the widest items use kStages stages");
 // Stages of the context ring for items of `span` sub-streams: a narrow item leaves each decoding
 // thread waiting on memory latency rather than on issue slots, so it needs more steps in flight.
 __host__ __device__ constexpr uint32_t ring_stages(uint32_t span) {
@@ -120,7 +126,7 @@ struct Smem {
                                                  // one set for the item being decoded, one being prepared
     Prepared prep[2];
     mps_bucket_tensor tensor[2];                 // descriptor of the item's tensor, copied by the scout
-    long long prefix[kPrefixCap + 1];
+    uint32_t stepofs[kMaxStages][kSS];           // element offset (row start + column) of every step of a stage
     unsigned long long full_bar[kMaxStages];     // bulk copies of a stage have landed
     unsigned long long empty_bar[kMaxStages];    // every warp is done reading a stage
     int32_t gid[256];                            // context -> table id of the staged tables
@@ -388,6 +394,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Returns false when the barrier did not complete within the spin limit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+#pragma unroll 1
     for (uint32_t i = 0; i < kSpinLimit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
@@ -527,16 +534,22 @@ __device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uin
         int good = 1;
         if (lane == 0) {
             good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u) ? 1 : 0;
-            if (good) mbar_expect_tx(full, nst * SPAN);
+            if (good) mbar_expect_tx(full, nst * SPAN);   // as early as possible: arming the barrier late costs the consumers dearly
         }
         good = __shfl_sync(0xFFFFFFFFu, good, 0);
         if (!good) return false;
+        // where every step of the block reads and writes: the consumers take the offset from here
+        // instead of tracking rows themselves; every lane releases its offset with its own arrive
+        uint32_t ofs = 0;
         if (lane < nst) {
             const uint32_t s = jb * kSS + lane;
             const uint32_t rr = s / spr, cc = (s - rr * spr) * it.k_eff;
-            const uint8_t* src = it.ctx_bytes + it.rowbase[rr < kRowCap ? rr : 0] + cc + it.t_begin;
-            bulk_g2s(smem_u32(sm.ctxring) + (stage * kSS + lane) * SPAN, src, SPAN, full);
+            ofs = it.rowbase[rr < kRowCap ? rr : 0] + cc;
+            sm.stepofs[stage][lane] = ofs;
         }
+        if (lane < (uint32_t)kSS) mbar_arrive(full);
+        if (lane < nst)
+            bulk_g2s(smem_u32(sm.ctxring) + (stage * kSS + lane) * SPAN, it.ctx_bytes + ofs + it.t_begin, SPAN, full);
     }
     return true;
 }
@@ -624,8 +637,11 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
     uint32_t hi[CH], acc[CH];
 #pragma unroll
     for (int c = 0; c < CH; ++c) acc[c] = 0;
+    uint16_t* const out0 = it.out + t0;
+#if !MPS_STEPOFS
     uint32_t c_rr = 0, c_cc = 0;
     uint16_t* outp = it.out + (it.rowbase[0] + t0);
+#endif
     const uint32_t nblocks = (it.nsteps + kSS - 1) / kSS;
 
     for (uint32_t jb = 0; jb < nblocks; ++jb) {
@@ -636,52 +652,71 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
         CT val[kSS];
 #pragma unroll
         for (int u = 0; u < kSS; ++u) val[u] = lds_ctx<CH>(ctx0 + (stage * kSS + u) * SPAN);
+        uint32_t ofs[kSS];   // element offset of every step's row position (written by the producer warp)
+        if (MPS_STEPOFS) {
+            static_assert(kSS == 8, "two 16-byte loads fetch a stage's step offsets");
+            const uint32_t so = smem_u32(&sm.stepofs[stage][0]);
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(ofs[0]), "=r"(ofs[1]), "=r"(ofs[2]), "=r"(ofs[3]) : "r"(so) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(ofs[4]), "=r"(ofs[5]), "=r"(ofs[6]), "=r"(ofs[7]) : "r"(so + 16u) : "memory");
+        }
+        // a whole block runs without per-step checks; only the last block of an item can be shorter
+        auto run_block = [&](auto checked) {
+            constexpr bool CHECKED = decltype(checked)::value;
 #pragma unroll
-        for (int u = 0; u < kSS; ++u) {
-            if ((uint32_t)u < count) {  // uniform; false only in the last block of an item
-                if (u % RP == 0) {
+            for (int u = 0; u < kSS; ++u) {
+                if (!CHECKED || (uint32_t)u < count) {
+                    if (u % RP == 0) {
+#pragma unroll
+                        for (int c = 0; c < CH; ++c) {
+                            hi[c] = schain_window(st.ch[c], ring0 + c * THREADS * kRingBytes, acc[c] & 0xFFFFu);
+                            acc[c] = 0;
+                        }
+                    }
+                    uint32_t e[CH];
 #pragma unroll
                     for (int c = 0; c < CH; ++c) {
-                        hi[c] = schain_window(st.ch[c], ring0 + c * THREADS * kRingBytes, acc[c] & 0xFFFFu);
-                        acc[c] = 0;
-                    }
-                }
-                uint32_t e[CH];
-#pragma unroll
-                for (int c = 0; c < CH; ++c) {
-                    // index = ctx << L | top L bits of the window, in one funnel shift
-                    const uint32_t idx = __funnelshift_l(hi[c], ctx_of<L>(Ctx<CH>::byte(val[u], c)), L);
-                    e[c] = lds_table(tbl + (idx << 2));
-                    if constexpr (!ESC) {
-                        hi[c] = __funnelshift_l(0u, hi[c], e[c]);  // shift by the low 5 bits = code length
-                        acc[c] += e[c];                            // low half accumulates the lengths
-                    } else {
-                        uint32_t used = e[c] & Entry<L>::kLenMask;
-                        if (e[c] & Entry<L>::kEsc) {                     // 16 raw bits follow the ESC code
-                            e[c] = __funnelshift_l(0u, hi[c], used) & 0xFFFF0000u;
-                            used += 16;
+                        // index = ctx << L | top L bits of the window, in one funnel shift
+                        const uint32_t idx = __funnelshift_l(hi[c], ctx_of<L>(Ctx<CH>::byte(val[u], c)), L);
+                        e[c] = lds_table(tbl + (idx << 2));
+                        if constexpr (!ESC) {
+                            hi[c] = __funnelshift_l(0u, hi[c], e[c]);  // shift by the low 5 bits = code length
+                            acc[c] += e[c];                            // low half accumulates the lengths
+                        } else {
+                            uint32_t used = e[c] & Entry<L>::kLenMask;
+                            if (e[c] & Entry<L>::kEsc) {                     // 16 raw bits follow the ESC code
+                                e[c] = __funnelshift_l(0u, hi[c], used) & 0xFFFF0000u;
+                                used += 16;
+                            }
+                            acc[c] = used;
                         }
-                        acc[c] = used;
                     }
-                }
-                store_syms<CH>(outp, e);
-                c_cc += it.k_eff;
-                outp += it.k_eff;
-                if (c_cc >= it.col_len) {  // next row of the bucket (uniform)
-                    c_cc = 0;
-                    ++c_rr;
-                    outp = it.out + (it.rowbase[c_rr < kRowCap ? c_rr : 0] + t0);
-                }
-                if ((CHK <= kSS) ? ((u + 1) % CHK == 0) : (u == kSS - 1 && (jb & 1u))) {
-                    // the position used for the request is the one of the last window; the bits consumed
-                    // since then (< 32) can only make the request one period late, which NEED allows for
+#if MPS_STEPOFS
+                    store_syms<CH>(out0 + ofs[u], e);
+#else
+                    store_syms<CH>(outp, e);
+                    c_cc += it.k_eff;
+                    outp += it.k_eff;
+                    if (c_cc >= it.col_len) {  // next row of the bucket (uniform)
+                        c_cc = 0;
+                        ++c_rr;
+                        outp = it.out + (it.rowbase[c_rr < kRowCap ? c_rr : 0] + t0);
+                    }
+#endif
+                    if ((CHK <= kSS) ? ((u + 1) % CHK == 0) : (u == kSS - 1 && (jb & 1u))) {
+                        // the position used for the request is the one of the last window; the bits consumed
+                        // since then (< 32) can only make the request one period late, which NEED allows for
 #pragma unroll
-                    for (int c = 0; c < CH; ++c) schain_request(st.ch[c], ring0 + c * THREADS * kRingBytes, it.bo);
-                    cp_async_commit();
-                    cp_async_wait<LAG>();
+                        for (int c = 0; c < CH; ++c) schain_request(st.ch[c], ring0 + c * THREADS * kRingBytes, it.bo);
+                        cp_async_commit();
+                        cp_async_wait<LAG>();
+                    }
                 }
             }
-        }
+        };
+        if (MPS_UNCHECKED && count == (uint32_t)kSS) run_block(std::false_type{});
+        else run_block(std::true_type{});
         __syncwarp();
         if ((tid & 31u) == 0) mbar_arrive(smem_u32(&sm.empty_bar[stage]));
     }
@@ -823,7 +858,7 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
 }
 
 template <int L, int THREADS, int CH>
-__device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws, int slot, bool prefix_cached,
+__device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws, int slot,
                               int wait_iter, int& q_cur, int& q_end) {
     constexpr int NCTX = (L == 7) ? 256 : 16;
     constexpr int TS = 1 << L;
@@ -860,11 +895,11 @@ __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws,
         int lo = 0, hi = args.count;  // largest ti with prefix[ti] <= item
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
-            const long long p = prefix_cached ? sm.prefix[mid] : args.item_prefix[mid];
+            const long long p = args.item_prefix[mid];
             if (p <= item) lo = mid; else hi = mid;
         }
         ti = lo;
-        local = item - (prefix_cached ? sm.prefix[ti] : args.item_prefix[ti]);
+        local = item - args.item_prefix[ti];
     }
     // the decoding warps read the descriptor from shared memory: a dependent chain of global loads at
     // the start of every item would be time nobody decodes in
@@ -964,21 +999,17 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
     constexpr int NCTX = (L == 7) ? 256 : 16;
     constexpr uint32_t SPAN = THREADS * CH;  // sub-streams per work item
-    constexpr int NT = THREADS + 64;         // decoding threads + producer warp + scout warp
     const int tid = threadIdx.x;
     const bool is_consumer = tid < THREADS;
     const bool is_producer = tid >= THREADS && tid < THREADS + 32;  // the whole producer warp
     const bool is_scout = tid >= THREADS + 32;       // the whole scout warp
 
-    const bool prefix_cached = args.tensors != nullptr && args.count <= kPrefixCap;
-    if (prefix_cached)
-        for (int i = tid; i <= args.count; i += NT) sm.prefix[i] = args.item_prefix[i];
     if (tid == 0) {
         sm.staged_tensor = -1;
         sm.abort = 0;
         sm.gid_taken = 0;
         for (int i = 0; i < kMaxStages; ++i) {
-            mbar_init(smem_u32(&sm.full_bar[i]), 1u);
+            mbar_init(smem_u32(&sm.full_bar[i]), 1u + kSS);  // lane 0's expect_tx + one arrive per step offset
             mbar_init(smem_u32(&sm.empty_bar[i]), THREADS / 32);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -986,7 +1017,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
     }
     __syncthreads();
     int q_cur = 0, q_end = 0;  // the scout's current grab from the work queue
-    if (is_scout) scout_prepare<L, THREADS, CH>(args, sm, ws, 0, prefix_cached, -1, q_cur, q_end);
+    if (is_scout) scout_prepare<L, THREADS, CH>(args, sm, ws, 0, -1, q_cur, q_end);
     __syncthreads();
 
     bool staged_esc = false;
@@ -998,7 +1029,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
         if (!P.valid) break;
         if (is_scout) {
             // next item's geometry, row bases and L2 prefetches, while the others decode this one
-            scout_prepare<L, THREADS, CH>(args, sm, ws, slot ^ 1, prefix_cached, iter + 1, q_cur, q_end);
+            scout_prepare<L, THREADS, CH>(args, sm, ws, slot ^ 1, iter + 1, q_cur, q_end);
         } else if (P.ok) {
             const int ti = P.ti, mode = P.mode;
             const mps_bucket_tensor& T = sm.tensor[slot];
