@@ -451,7 +451,10 @@ struct SChain {
 __device__ __forceinline__ uint32_t schain_window(SChain& ch, uint32_t ring, uint32_t used) {
     const uint32_t np = ch.pos + used;
     const uint32_t moved = np ^ ch.pos;
-    const uint32_t addr = ring_unit_addr(ring, (np >> 5) + 1);
+    // byte address of unit (np >> 5) + 1 in the ring: units are 4 bytes, swapped in pairs (^4), ring of 64 bytes
+    uint32_t addr;
+    asm("lop3.b32 %0, %1, 4, 60, 0x28;" : "=r"(addr) : "r"((np >> 3) + 4u));  // (x ^ 4) & 60
+    addr += ring;
     ch.pos = np;
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.gt.u32 p, %2, 31;\n\t@p mov.u32 %0, %1;\n\t@p ld.shared.u32 %1, [%3];\n\t}"
@@ -693,7 +696,9 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                         }
                     }
 #if MPS_STEPOFS
-                    store_syms<CH>(out0 + ofs[u], e);
+                    uint16_t* dst;   // out0 + ofs[u] elements, as one multiply-add
+                    asm("mad.wide.u32 %0, %1, 2, %2;" : "=l"(dst) : "r"(ofs[u]), "l"(out0));
+                    store_syms<CH>(dst, e);
 #else
                     store_syms<CH>(outp, e);
                     c_cc += it.k_eff;
