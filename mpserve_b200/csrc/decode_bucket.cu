@@ -57,15 +57,6 @@ constexpr int kSS = 8;                // steps per stage of the streaming path's
 #ifndef MPS_LOOK
 #define MPS_LOOK 1
 #endif
-#ifndef MPS_UNCHECKED
-#define MPS_UNCHECKED 1
-#endif
-#ifndef MPS_STEPOFS
-#define MPS_STEPOFS 1
-#endif
-#ifndef MPS_COOP_BEGIN
-#define MPS_COOP_BEGIN 1
-#endif
 #ifndef MPS_NO_STREAM
 #define MPS_NO_STREAM 0
 #endif
@@ -579,15 +570,6 @@ __device__ __forceinline__ void stream_begin(Smem& sm, const StreamItem& it, Str
         st.ch[c].pos = pos;
         st.ch[c].next = (pos >> 7) + kRingChunks;
     }
-#if !MPS_COOP_BEGIN
-#pragma unroll
-    for (int c = 0; c < CH; ++c)
-#pragma unroll
-        for (int q = 0; q < kRingChunks; ++q)
-            chunk_fetch(rings + (c * THREADS + tid) * kRingBytes, it.bo, ((st.ch[c].pos >> 7) + q) << 4);
-    cp_async_commit();
-    return;
-#endif
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
 #pragma unroll
@@ -641,10 +623,6 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
 #pragma unroll
     for (int c = 0; c < CH; ++c) acc[c] = 0;
     uint16_t* const out0 = it.out + t0;
-#if !MPS_STEPOFS
-    uint32_t c_rr = 0, c_cc = 0;
-    uint16_t* outp = it.out + (it.rowbase[0] + t0);
-#endif
     const uint32_t nblocks = (it.nsteps + kSS - 1) / kSS;
 
     for (uint32_t jb = 0; jb < nblocks; ++jb) {
@@ -656,7 +634,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
 #pragma unroll
         for (int u = 0; u < kSS; ++u) val[u] = lds_ctx<CH>(ctx0 + (stage * kSS + u) * SPAN);
         uint32_t ofs[kSS];   // element offset of every step's row position (written by the producer warp)
-        if (MPS_STEPOFS) {
+        {
             static_assert(kSS == 8, "two 16-byte loads fetch a stage's step offsets");
             const uint32_t so = smem_u32(&sm.stepofs[stage][0]);
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -695,20 +673,9 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                             acc[c] = used;
                         }
                     }
-#if MPS_STEPOFS
                     uint16_t* dst;   // out0 + ofs[u] elements, as one multiply-add
                     asm("mad.wide.u32 %0, %1, 2, %2;" : "=l"(dst) : "r"(ofs[u]), "l"(out0));
                     store_syms<CH>(dst, e);
-#else
-                    store_syms<CH>(outp, e);
-                    c_cc += it.k_eff;
-                    outp += it.k_eff;
-                    if (c_cc >= it.col_len) {  // next row of the bucket (uniform)
-                        c_cc = 0;
-                        ++c_rr;
-                        outp = it.out + (it.rowbase[c_rr < kRowCap ? c_rr : 0] + t0);
-                    }
-#endif
                     if ((CHK <= kSS) ? ((u + 1) % CHK == 0) : (u == kSS - 1 && (jb & 1u))) {
                         // the position used for the request is the one of the last window; the bits consumed
                         // since then (< 32) can only make the request one period late, which NEED allows for
@@ -720,7 +687,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                 }
             }
         };
-        if (MPS_UNCHECKED && count == (uint32_t)kSS) run_block(std::false_type{});
+        if (count == (uint32_t)kSS) run_block(std::false_type{});
         else run_block(std::true_type{});
         __syncwarp();
         if ((tid & 31u) == 0) mbar_arrive(smem_u32(&sm.empty_bar[stage]));
