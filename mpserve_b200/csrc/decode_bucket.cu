@@ -74,7 +74,7 @@ struct BatchArgs {
 #define MPS_STAGES 3
 #endif
 constexpr int kStages = MPS_STAGES;            // context-byte ring: stages of kSS steps each for the widest items
-constexpr int kMaxStages = 8;                  // narrower items split the same ring into more stages
+constexpr int kMaxStages = 4;                  // narrower items split the same ring into more stages
 static_assert(kMaxStages >= kStages, "the widest items use kStages stages");
 // Stages of the context ring for items of `span` sub-streams: a narrow item leaves each decoding
 // thread waiting on memory latency rather than on issue slots, so it needs more steps in flight.
@@ -118,6 +118,8 @@ struct Smem {
     Prepared prep[2];
     mps_bucket_tensor tensor[2];                 // descriptor of the item's tensor, copied by the scout
     uint32_t stepofs[kMaxStages][kSS];           // element offset (row start + column) of every step of a stage
+    uint32_t stepofs_b[kMaxStages][kSS];         // same for the sub-streams of a step that already sit in the next row
+    uint32_t stepsplit[kMaxStages][kSS];         // first local sub-stream of a step that sits in the next row
     unsigned long long full_bar[kMaxStages];     // bulk copies of a stage have landed
     unsigned long long empty_bar[kMaxStages];    // every warp is done reading a stage
     int32_t gid[256];                            // context -> table id of the staged tables
@@ -507,7 +509,10 @@ struct StreamItem {
     const uint32_t* startbit;
     const uint32_t* rowbase;
     BitOrigin bo;
-    uint32_t t_begin, k_eff, col_len, nsteps;
+    uint32_t t_begin, k_eff, col_len;
+    uint32_t nsteps;       // steps of this item, a ragged last one included
+    uint32_t nfull;        // steps in which every sub-stream of the bucket has an element
+    uint32_t last_active;  // local sub-streams that have an element in the ragged last step (0: there is none)
 };
 
 // Producer warp.  Lane 0 waits until every consumer warp has released the stage and arms its "full"
@@ -515,11 +520,11 @@ struct StreamItem {
 // one step), so a block of steps costs the producer one round of address arithmetic, not kSS rounds
 // back to back.  The producer never decodes, so consumers are never held back by a slow sibling: they
 // only ever wait for data.  Returns false if a stage never freed.
-template <int SPAN>
+template <int SPAN, bool SPLIT>
 __device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uint32_t blk, uint32_t nblocks) {
     constexpr uint32_t NST = ring_stages(SPAN);
     const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t spr = it.col_len / it.k_eff;  // steps per row of the bucket (col_len is a multiple of k_eff here)
+    const uint32_t spr = SPLIT ? 1u : it.col_len / it.k_eff;  // steps per row when rows hold whole steps
     for (uint32_t jb = 0; jb < nblocks; ++jb) {
         const uint32_t g = blk + jb, stage = g % NST, round = g / NST;
         const uint32_t full = smem_u32(&sm.full_bar[stage]);
@@ -528,22 +533,48 @@ __device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uin
         int good = 1;
         if (lane == 0) {
             good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u) ? 1 : 0;
-            if (good) mbar_expect_tx(full, nst * SPAN);   // as early as possible: arming the barrier late costs the consumers dearly
+            uint32_t bytes = nst * SPAN;
+            if (SPLIT && it.nsteps > it.nfull && jb * kSS + nst == it.nsteps) bytes -= SPAN - it.last_active;  // ragged last step
+            if (good) mbar_expect_tx(full, bytes);   // as early as possible: arming the barrier late costs the consumers dearly
         }
         good = __shfl_sync(0xFFFFFFFFu, good, 0);
         if (!good) return false;
         // where every step of the block reads and writes: the consumers take the offset from here
-        // instead of tracking rows themselves; every lane releases its offset with its own arrive
-        uint32_t ofs = 0;
-        if (lane < nst) {
-            const uint32_t s = jb * kSS + lane;
-            const uint32_t rr = s / spr, cc = (s - rr * spr) * it.k_eff;
-            ofs = it.rowbase[rr < kRowCap ? rr : 0] + cc;
-            sm.stepofs[stage][lane] = ofs;
+        // instead of tracking rows themselves; every lane releases its offsets with its own arrive
+        const uint32_t dst = smem_u32(sm.ctxring) + (stage * kSS + lane) * SPAN;
+        if constexpr (!SPLIT) {
+            uint32_t ofs = 0;
+            if (lane < nst) {
+                const uint32_t s = jb * kSS + lane;
+                const uint32_t rr = s / spr, cc = (s - rr * spr) * it.k_eff;
+                ofs = it.rowbase[rr < kRowCap ? rr : 0] + cc;
+                sm.stepofs[stage][lane] = ofs;
+            }
+            if (lane < (uint32_t)kSS) mbar_arrive(full);
+            if (lane < nst) bulk_g2s(dst, it.ctx_bytes + ofs + it.t_begin, SPAN, full);
+        } else {
+            // rows do not hold whole steps: a step may start in one row and end in the next (never further:
+            // rows are at least as long as a step), so it is two copies and two offsets
+            uint32_t ofs_a = 0, ofs_b = 0, part_a = 0, part_b = 0;
+            if (lane < nst) {
+                const uint32_t s = jb * kSS + lane;
+                const unsigned long long e0 = (unsigned long long)s * it.k_eff;
+                const uint32_t rr = (uint32_t)(e0 / it.col_len), cc = (uint32_t)(e0 - (unsigned long long)rr * it.col_len);
+                const uint32_t act = (s < it.nfull) ? SPAN : it.last_active;       // sub-streams with an element in this step
+                const uint32_t room = it.col_len - cc;                               // sub-streams 0..room-1 stay in row rr
+                const uint32_t split = room > it.t_begin ? (room - it.t_begin < SPAN ? room - it.t_begin : SPAN) : 0u;
+                ofs_a = it.rowbase[rr < kRowCap ? rr : 0] + cc;
+                ofs_b = it.rowbase[rr + 1 < kRowCap ? rr + 1 : 0] + cc - it.col_len;
+                part_a = split < act ? split : act;
+                part_b = act - part_a;
+                sm.stepofs[stage][lane] = ofs_a;
+                sm.stepofs_b[stage][lane] = ofs_b;
+                sm.stepsplit[stage][lane] = split;
+            }
+            if (lane < (uint32_t)kSS) mbar_arrive(full);
+            if (part_a) bulk_g2s(dst, it.ctx_bytes + ofs_a + it.t_begin, part_a, full);
+            if (part_b) bulk_g2s(dst + part_a, it.ctx_bytes + ofs_b + it.t_begin + part_a, part_b, full);
         }
-        if (lane < (uint32_t)kSS) mbar_arrive(full);
-        if (lane < nst)
-            bulk_g2s(smem_u32(sm.ctxring) + (stage * kSS + lane) * SPAN, it.ctx_bytes + ofs + it.t_begin, SPAN, full);
     }
     return true;
 }
@@ -583,7 +614,7 @@ __device__ __forceinline__ void stream_begin(Smem& sm, const StreamItem& it, Str
     cp_async_commit();
 }
 
-template <int L, int THREADS, int CH, bool ESC>
+template <int L, int THREADS, int CH, bool ESC, bool SPLIT>
 __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st,
                                            uint32_t blk) {
     constexpr int RP = ESC ? 1 : ((32 - L) / L + 1);   // symbols per 32-bit window
@@ -642,6 +673,19 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                          : "=r"(ofs[4]), "=r"(ofs[5]), "=r"(ofs[6]), "=r"(ofs[7]) : "r"(so + 16u) : "memory");
         }
+        uint32_t ofs_b[kSS], split[kSS];   // rows that do not hold whole steps: see producer_run
+        if constexpr (SPLIT) {
+            const uint32_t sb = smem_u32(&sm.stepofs_b[stage][0]), sx = smem_u32(&sm.stepsplit[stage][0]);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(ofs_b[4 * h]), "=r"(ofs_b[4 * h + 1]), "=r"(ofs_b[4 * h + 2]), "=r"(ofs_b[4 * h + 3])
+                             : "r"(sb + 16u * h) : "memory");
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(split[4 * h]), "=r"(split[4 * h + 1]), "=r"(split[4 * h + 2]), "=r"(split[4 * h + 3])
+                             : "r"(sx + 16u * h) : "memory");
+            }
+        }
         // a whole block runs without per-step checks; only the last block of an item can be shorter
         auto run_block = [&](auto checked) {
             constexpr bool CHECKED = decltype(checked)::value;
@@ -673,9 +717,13 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                             acc[c] = used;
                         }
                     }
-                    uint16_t* dst;   // out0 + ofs[u] elements, as one multiply-add
-                    asm("mad.wide.u32 %0, %1, 2, %2;" : "=l"(dst) : "r"(ofs[u]), "l"(out0));
-                    store_syms<CH>(dst, e);
+                    uint32_t o = ofs[u];
+                    if constexpr (SPLIT) o = (tid * CH >= split[u]) ? ofs_b[u] : o;
+                    uint16_t* dst;   // out0 + o elements, as one multiply-add
+                    asm("mad.wide.u32 %0, %1, 2, %2;" : "=l"(dst) : "r"(o), "l"(out0));
+                    bool mine = true;   // the ragged last step holds an element for the first sub-streams only
+                    if constexpr (SPLIT && CHECKED) mine = (jb * kSS + u < it.nfull) || (tid * CH < it.last_active);
+                    if (mine) store_syms<CH>(dst, e);
                     if ((CHK <= kSS) ? ((u + 1) % CHK == 0) : (u == kSS - 1 && (jb & 1u))) {
                         // the position used for the request is the one of the last window; the bits consumed
                         // since then (< 32) can only make the request one period late, which NEED allows for
@@ -687,7 +735,8 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                 }
             }
         };
-        if (count == (uint32_t)kSS) run_block(std::false_type{});
+        // (the block that holds a ragged last step always takes the checked form)
+        if (count == (uint32_t)kSS && !(SPLIT && it.last_active != 0u && jb + 1 == nblocks)) run_block(std::false_type{});
         else run_block(std::true_type{});
         __syncwarp();
         if ((tid & 31u) == 0) mbar_arrive(smem_u32(&sm.empty_bar[stage]));
@@ -1021,7 +1070,10 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             StreamItem it;
             StreamThread<L, THREADS, CH> st;
             bool stream = false;
-            if (vec && P.rows_al16 && t_begin + SPAN <= k_eff && (col_len % k_eff) == 0 && (k_eff % 16u) == 0 &&
+            // rows that hold whole steps, or rows at least one step long whose length keeps 16-byte alignment
+            const bool split = (col_len % k_eff) != 0;
+            if (vec && P.rows_al16 && t_begin + SPAN <= k_eff && (k_eff % 16u) == 0 &&
+                (!split || (col_len > k_eff && (col_len % 16) == 0 && total < 0xFFFFFFFFLL)) &&
                 ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & 15u) == 0) && !MPS_NO_STREAM) {
                 const uint8_t* bucket_bytes = reinterpret_cast<const uint8_t*>(T.bitstream) + 8 * wb;
                 const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(bucket_bytes) & 15u);  // 0 or 8
@@ -1034,7 +1086,10 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                     it.bo.base = bucket_bytes - mis; it.bo.last_ofs = (uint32_t)((valid - 16) & ~15LL); it.bo.bit_delta = 8 * mis;
                     it.bo.tail_ofs = (valid & 8) ? it.bo.last_ofs + 16u : 0xFFFFFFFFu;
                     it.t_begin = t_begin; it.k_eff = k_eff; it.col_len = (uint32_t)col_len;
-                    it.nsteps = (uint32_t)(total / k_eff);
+                    it.nfull = (uint32_t)(total / k_eff);
+                    const uint32_t rem = (uint32_t)(total - (long long)it.nfull * k_eff);  // sub-streams with one more element
+                    it.last_active = rem > t_begin ? (rem - t_begin < SPAN ? rem - t_begin : SPAN) : 0u;
+                    it.nsteps = it.nfull + (it.last_active ? 1u : 0u);
                 }
             }
             MPS_TICK(0);  // geometry
@@ -1042,7 +1097,8 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             uint32_t nblocks = 0;
             if (stream) nblocks = (it.nsteps + kSS - 1) / kSS;
             if (is_producer) {
-                if (stream) run_ok = producer_run<SPAN>(sm, it, blk, nblocks);
+                if (stream) run_ok = split ? producer_run<SPAN, true>(sm, it, blk, nblocks)
+                                           : producer_run<SPAN, false>(sm, it, blk, nblocks);
             } else if (is_consumer) {
                 if (stream) stream_begin<L, THREADS, CH>(sm, it, st);
                 MPS_TICK(2);  // async copies started
@@ -1077,8 +1133,12 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                 // ---- decode --------------------------------------------------------------------------
                 const uint32_t t0 = t_begin + (uint32_t)tid * CH;
                 if (stream) {
-                    run_ok = staged_esc ? stream_run<L, THREADS, CH, true>(sm, it, st, blk)
-                                        : stream_run<L, THREADS, CH, false>(sm, it, st, blk);
+                    if (split)
+                        run_ok = staged_esc ? stream_run<L, THREADS, CH, true, true>(sm, it, st, blk)
+                                            : stream_run<L, THREADS, CH, false, true>(sm, it, st, blk);
+                    else
+                        run_ok = staged_esc ? stream_run<L, THREADS, CH, true, false>(sm, it, st, blk)
+                                            : stream_run<L, THREADS, CH, false, false>(sm, it, st, blk);
                 } else if (vec) {
                     if (t0 < k_eff) {
                         if (staged_esc)

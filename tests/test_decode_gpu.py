@@ -105,6 +105,14 @@ FP8_SEEDED = [
     (2048, 256, "normal", "tensor", 64),        # small k
     (1024, 1024, "normal", "tensor", 1),        # k = 1
     (512, 768, "normal", "channel", 32),
+    # rows that do not hold a whole number of steps (m % k != 0): a step spans two rows, and the last step
+    # of a bucket may be ragged
+    (300, 3584, "normal", "channel", 1024),
+    (200, 1536, "normal", "tensor", 1024),
+    (77, 2064, "student_t", "channel", 1024),
+    (130, 1040, "normal", "tensor", 1024),
+    (64, 400, "normal", "tensor", 256),
+    (256, 3584, "student_t", "tensor", 512),
 ]
 
 
