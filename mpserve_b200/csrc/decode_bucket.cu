@@ -1014,6 +1014,7 @@ __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws,
 }
 
 template <int L, int THREADS, int CH>
+// (registers are handed out to a CTA four warps at a time, so 320 threads get what 384 would: 168 each)
 __global__ void __launch_bounds__(THREADS + 64, 1)
 bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __restrict__ ws) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
