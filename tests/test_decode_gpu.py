@@ -142,7 +142,7 @@ def test_fp8_esc_large(dev, force_config):
 
 
 def test_fp8_config1_full_size_roundtrip(dev):
-    """BASELINE config 1 at full size: 4096x4096, N(0,0.02), per-tensor scale, k=1024."""
+    """One 4096x4096 linear weight at full size, N(0,0.02), per-tensor scale, k=1024."""
     n = m = 4096
     c = wl.quantize_fp8(wl.random_weight(n, m, 0, "normal"), "tensor")
     art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
