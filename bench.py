@@ -173,7 +173,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "u16", "data": "synthetic",
-        "config": {"workload": f"{wname} fp8-e4m3 per-channel + huffman sidecar (L=7,k=1024), tp={tp}",
+        "config": {"workload": f"{wname} fp8-e4m3 per-channel + huffman sidecar (L=7,k=1024), tp={tp}, layers={layers}",
                    "note": "the reference has no CPU decoder; this is the CPU port of its decode kernel "
                            "(ESC honoured), OpenMP over buckets x sub-streams; bounded sample per step"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
