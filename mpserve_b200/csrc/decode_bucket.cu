@@ -791,8 +791,8 @@ __device__ void decode_generic(const Smem& sm, const uint32_t* rowbase, const mp
 // The raw tables of a bucket (up to 80 KB) usually come straight from HBM, so every thread first
 // issues a whole batch of independent 16-byte + 4-byte loads and only then converts them: the batch,
 // not a single load, is what waits for memory.
-template <int L, int THREADS>
-__device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& T, int tid) {
+template <int L, int THREADS, typename F>
+__device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& T, int tid, F&& after_first_loads) {
     constexpr int TS = 1 << L;                 // entries per table
     constexpr int GROUPS_PER_CTX = TS / 8;     // 8 entries per thread-iteration
     constexpr int NGROUPS = kTableEntries / 8;
@@ -830,6 +830,7 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
                 }
             }
         }
+        if (it0 == 0) after_first_loads();
 #pragma unroll
         for (int q = 0; q < BATCH; ++q) {
             const int g = tid + (it0 + q) * THREADS;
@@ -1101,10 +1102,9 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                 if (stream) run_ok = split ? producer_run<SPAN, true>(sm, it, blk, nblocks)
                                            : producer_run<SPAN, false>(sm, it, blk, nblocks);
             } else if (is_consumer) {
-                if (stream) stream_begin<L, THREADS, CH>(sm, it, st);
-                MPS_TICK(2);  // async copies started
-
                 // ---- tables: restage only when the context->table map changed ------------------------
+                // The first chunks of the bitstream are requested right after the first batch of table
+                // loads: both wait on memory, and the table loads are the ones the threads need first.
                 constexpr int CPT = (NCTX + THREADS - 1) / THREADS;  // contexts per thread
                 int differs = (sm.staged_tensor != ti);
                 int32_t my_gid[CPT];
@@ -1127,9 +1127,11 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                     }
                     if (tid == 0) sm.staged_tensor = ti;
                     group_sync(THREADS);
-                    staged_esc = stage_tables<L, THREADS>(sm, T, tid);
+                    staged_esc = stage_tables<L, THREADS>(sm, T, tid, [&] { if (stream) stream_begin<L, THREADS, CH>(sm, it, st); });
+                } else if (stream) {
+                    stream_begin<L, THREADS, CH>(sm, it, st);
                 }
-                MPS_TICK(3);  // tables
+                MPS_TICK(3);  // tables and first chunks
 
                 // ---- decode --------------------------------------------------------------------------
                 const uint32_t t0 = t_begin + (uint32_t)tid * CH;
