@@ -38,7 +38,7 @@ UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one bucket_decode_kernel launch divided by its elements, from
 # the ncu capture summarised in profiles/ (a 218 M-element launch; traffic grows in proportion to the elements)
-NCU_TRAFFIC_BYTES_PER_ELEMENT = 3.763
+NCU_TRAFFIC_BYTES_PER_ELEMENT = 3.757
 
 
 def log(*a):
