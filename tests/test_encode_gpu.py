@@ -177,3 +177,22 @@ def test_build_then_decode_roundtrip_on_device():
     out = MPServe_cuda.huffman_decode_fp8(*util.decode_fp8_args(c.fp8_u8.to(dev), art, n, m, 7))
     torch.cuda.synchronize()
     assert torch.equal(out.cpu().view(torch.uint16), c.bf16.view(torch.uint16))
+
+
+@pytest.mark.parametrize("n,m,k", [(14336, 4096, 1024),    # widest weight of an 8B-shaped layer
+                                   (8192, 3584, 1024),     # row-parallel shard whose rows do not hold whole steps
+                                   (4096, 4096, 256)])     # the reference builder's default sub-stream count
+def test_full_size_build_decode_checksum_on_device(n, m, k):
+    """Full-size tensors, everything on the GPU: the builder's sidecar decodes back to the source bit for
+    bit (a lossless round trip does not depend on the size), and the device checksum agrees with torch."""
+    import MPServe_cuda
+    from mpserve_b200 import api, util
+
+    dev = torch.device("cuda:0")
+    c = wl.quantize_fp8(wl.random_weight(n, m, 4242, "normal", device=dev), "channel")
+    art = MPServe_cuda.huffman_build_fp8_decode_tables(c.bf16, c.fp8_u8, c.scales_u16, max_len=7, threads_per_block=k)
+    out = MPServe_cuda.huffman_decode_fp8(*util.decode_fp8_args(c.fp8_u8, art, n, m, 7))
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.uint16), c.bf16.view(torch.uint16))
+    acc = api.checksum_u16(out)
+    assert int(acc.cpu()[0]) % (1 << 64) == int(c.bf16.view(torch.uint16).to(torch.int64).sum()) % (1 << 64)
