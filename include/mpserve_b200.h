@@ -49,6 +49,12 @@ MPS_API int64_t mps_cuda_clock_rate_khz(void);
  * the kernels leave it zeroed again.  Two calls that may overlap on the GPU need two workspaces. */
 MPS_API size_t mps_workspace_bytes(void);
 
+/* Every wait inside the decode kernels is bounded; a kernel whose wait ran out stops taking work and
+ * records it in the workspace.  This call waits for the stream, reports whether any launch since the
+ * last query gave up (*timed_out = 1; its outputs are then incomplete) and clears the record.  The
+ * reference has no counterpart: its kernels have no waits. */
+MPS_API int mps_decode_status(void* workspace, size_t workspace_bytes, void* stream, int32_t* timed_out);
+
 /* One compressed tensor (all pointers device) ---------------------------------------------------
  * mode 0: FP8 rectangular buckets, L=7, 256 contexts   (huffman_decode_fp8_entry)
  * mode 1: AWQ-INT4 rectangular buckets, L=11, 16 ctx   (huffman_decode_awq_int4_bucket_entry)

@@ -22,7 +22,7 @@ __all__ = [
     "huffman_decode_awq_int4_bucket_by_scale", "huffman_decode_awq_shared_table",
     "huffman_build_fp8_decode_tables", "huffman_build_awq_int4_bucket_decode_tables",
     "huffman_build_awq_int4_bucket_decode_tables_by_scale", "huffman_build_awq_decode_tables",
-    "BucketDecodePlan", "checksum_u16",
+    "BucketDecodePlan", "checksum_u16", "decode_timed_out",
 ]
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
@@ -59,6 +59,17 @@ def _same_device(tensors: Sequence[torch.Tensor]) -> torch.device:
         if t.device != dev:
             raise ValueError("all tensors must be on the same CUDA device")
     return dev
+
+
+def decode_timed_out(device: torch.device | None = None) -> bool:
+    """Waits for the current stream and tells whether a decode launched on it since the last call gave
+    up on one of its bounded waits (its outputs are then incomplete).  Always False in normal operation."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        ws = _workspace(dev)
+        flag = C.c_int32(0)
+        _lib.check(_lib.load().mps_decode_status(ws.data_ptr(), ws.numel() * 4, _stream_ptr(dev), C.byref(flag)))
+    return bool(flag.value)
 
 
 def cuda_clock_rate_khz() -> int:

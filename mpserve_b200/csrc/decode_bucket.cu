@@ -1452,6 +1452,18 @@ int64_t mps_cuda_clock_rate_khz(void) {
 
 size_t mps_workspace_bytes(void) { return 256; }
 
+int mps_decode_status(void* workspace, size_t workspace_bytes, void* stream, int32_t* timed_out) {
+    if (!workspace || workspace_bytes < mps_workspace_bytes() || !timed_out) { set_error("mps_decode_status: bad argument"); return MPS_ERR_INVALID; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned int* ws = static_cast<unsigned int*>(workspace);
+    unsigned int flag = 0;
+    MPS_CUDA_TRY(cudaMemcpyAsync(&flag, ws + 2, sizeof(flag), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    if (flag) MPS_CUDA_TRY(cudaMemsetAsync(ws + 2, 0, sizeof(flag), st));
+    *timed_out = flag ? 1 : 0;
+    return MPS_OK;
+}
+
 int mps_decode_fp8(const uint8_t* fp8_u8, const uint64_t* bitstream_u64, int64_t bitstream_words,
                    const uint16_t* decode_syms_u16, const uint8_t* decode_lens_u8, int64_t num_tables,
                    const int32_t* bucket_table_i32, const int32_t* bucket_col_start_i32,

@@ -25,7 +25,7 @@ def _declared():
 def test_header_declares_entry_points():
     names = _declared()
     for must in ("mps_decode_fp8", "mps_decode_awq_int4_bucket", "mps_decode_awq_int4_bucket_by_scale",
-                 "mps_decode_awq_shared_table", "mps_decode_bucket_batch", "mps_decode_bucket_tensor", "mps_checksum_u16"):
+                 "mps_decode_awq_shared_table", "mps_decode_bucket_batch", "mps_decode_bucket_tensor", "mps_decode_status", "mps_checksum_u16"):
         assert must in names
 
 

@@ -150,6 +150,16 @@ def test_fp8_config1_full_size_roundtrip(dev):
     np.testing.assert_array_equal(got, _u16(c.bf16))
 
 
+def test_no_bounded_wait_runs_out_in_normal_operation(dev):
+    """Waits in the kernels are bounded and report through the workspace; nothing may report here."""
+    n, m = 512, 2048
+    c = wl.quantize_fp8(wl.random_weight(n, m, 21, "normal"), "tensor")
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
+    for _ in range(3):
+        np.testing.assert_array_equal(_fp8_decode(c.fp8_u8.numpy(), art, n, m, dev), _u16(c.bf16))
+    assert api.decode_timed_out(dev) is False
+
+
 def test_fp8_repeated_calls_reuse_workspace(dev):
     n, m = 256, 1024
     c = wl.quantize_fp8(wl.random_weight(n, m, 3, "normal"), "channel")
