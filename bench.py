@@ -2,17 +2,27 @@
 """Benchmark of the hot path: FP8 checkpoint + Huffman sidecar -> BF16 weights on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload model|single|sizes|awq] [--layers L]
 
-One "step" decompresses every linear weight of the workload once (one persistent-kernel launch per
-rank).  N=1: Llama-3-8B-shaped random-init weights, per-channel FP8-E4M3 scales (all 32 layers, 224
-tensors, 6.98 G elements).  N>1 (launched by torchrun, one rank per GPU): Llama-3-70B-shaped weights,
-tensor-parallel sharded N ways, each rank decoding only its own shards, with the layer count chosen
-so that the work per GPU stays that of the N=1 run (weak scaling); there is no collective in the
-timed region, NCCL only reduces the timing and the final checksum.
+``--workload model`` (the default, what the round-end driver runs).  One "step" decompresses every
+linear weight of the workload once (one persistent-kernel launch per rank).  N=1: Llama-3-8B-shaped
+random-init weights, per-channel FP8-E4M3 scales (all 32 layers, 224 tensors, 6.98 G elements).  N>1
+(launched by torchrun, one rank per GPU): Llama-3-70B-shaped weights, all 80 layers, tensor-parallel
+sharded N ways, each rank decoding only its own shards (the total work is fixed, so ``scaling`` is
+"strong"; ``--layers`` shortens the model for quick runs).  There is no collective in the timed
+region; NCCL only reduces the timings and, afterwards, the checksum of all ranks' outputs.
 
-Rank 0 prints ONE JSON line.  `value` is decompressed BF16 GB/s (2*n*m bytes per tensor) with
-compressed inputs resident in HBM; `e2e` includes the host->device copy of the compressed inputs
-from pinned memory and the read-back of the checksum.
+``--workload single | sizes | awq`` (N=1) time one tensor per call through the per-tensor entry
+points the reference's plugin calls: a lone 4096x4096 weight with a per-tensor scale; single tensors
+from 64 KB to 1 GB of output, N(0, 0.02) and Student-t(4); the Llama-3-8B linears as INT4 (group 128)
+in the three AWQ sidecar layouts.  L2 is flushed before every timed call.
+
+Rank 0 prints ONE JSON line.  ``value`` is decompressed BF16 GB/s (2*n*m bytes per tensor) with
+compressed inputs resident in HBM; ``e2e`` includes the host->device copy of the compressed inputs
+from pinned memory and the read-back of the checksum; ``dropin`` is the same step made of one
+``MPServe_cuda.huffman_decode_fp8`` call per weight, each returning a fresh tensor, as the
+reference's plugin does.  ``--impl reference`` times the CPU decode of the same format on all host
+cores of rank 0 (the other ranks exit).
 """
 from __future__ import annotations
 
@@ -36,13 +46,42 @@ from mpserve_b200 import workloads as wl  # noqa: E402
 METRIC = "decompressed_bf16_gbps"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one bucket_decode_kernel launch divided by its elements, from
-# the ncu capture summarised in profiles/ (a 218 M-element launch; traffic grows in proportion to the elements)
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch divided by its elements, from the ncu
+# capture summarised in profiles/ (traffic grows in proportion to the elements of a launch)
 NCU_TRAFFIC_BYTES_PER_ELEMENT = 3.757
+E2E_MAX_PINNED_BYTES = 24 << 30   # pinned host memory one rank may take for the end-to-end leg
+
+DECODE_KEYS = ("bitstream_u64", "decode_syms_u16", "decode_lens_u8", "bucket_table_i32", "bucket_col_start_i32",
+               "bucket_col_len_i32", "bucket_row_offsets_i32", "row_indices_i32", "bucket_thread_startbit_u32",
+               "bucket_bit_base_i64")
+SHARED_KEYS = ("bitstream_u64", "decode_syms_i16", "decode_nbits_u8", "scale_bit_base_i64", "chunk_startbit_rel_u32",
+               "chunk_out_base_u32", "chunk_meta_u32", "chunk_scale_id_i32", "out_idx_i32", "stream_chunk_ofs_i64",
+               "stream_chunk_ids_i32")
+BYSCALE_KEYS = ("bitstream_u64", "decode_syms_u16", "decode_lens_u8", "bucket_table_i32", "bucket_group_offsets_i32",
+                "group_rows_i32", "group_col_start_i32", "bucket_thread_startbit_u32", "bucket_bit_base_i64")
+SIZES = [(128, 256), (256, 512), (512, 1024), (1024, 2048), (2048, 4096), (4096, 4096), (8192, 8192), (16384, 8192),
+         (16384, 16384), (32768, 16384)]     # 64 KB ... 1 GB of BF16
 
 
 def log(*a):
     print(*a, file=sys.stderr, flush=True)
+
+
+def hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def cpu_model() -> str:
+    try:
+        for line in Path("/proc/cpuinfo").read_text().splitlines():
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
 
 
 # ------------------------------------------------------------------------------------------------
@@ -52,15 +91,16 @@ def log(*a):
 def workload_for(n_gpus: int, layers_override: int | None):
     if n_gpus == 1:
         cfg, tp, name = wl.LLAMA3_8B, 1, "llama3-8b-shaped"
-        layers = cfg["layers"]
     else:
         cfg, tp, name = wl.LLAMA3_70B, n_gpus, "llama3-70b-shaped"
-        per_layer = sum(n * m for _, n, m in wl.layer_linears(cfg)) / tp
-        target = sum(n * m for _, n, m in wl.layer_linears(wl.LLAMA3_8B)) * wl.LLAMA3_8B["layers"]
-        layers = max(1, min(cfg["layers"], int(round(target / per_layer))))
+    layers = cfg["layers"]
     if layers_override:
-        layers = layers_override
+        layers = min(layers, layers_override)
     return cfg, tp, name, layers
+
+
+def workload_text(wname, tp, layers) -> str:
+    return f"{wname} fp8-e4m3 per-channel + huffman sidecar (L=7,k=1024), tp={tp}, layers={layers}"
 
 
 def encode_layer_cpu(cfg, tp, rank, seed_base):
@@ -76,16 +116,6 @@ def encode_layer_cpu(cfg, tp, rank, seed_base):
         art = orc.build_fp8(c.bf16.view(torch.uint16).numpy(), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
         out.append((name, sn, sm, c, art))
     return out
-
-
-DECODE_KEYS = ("bitstream_u64", "decode_syms_u16", "decode_lens_u8", "bucket_table_i32", "bucket_col_start_i32",
-               "bucket_col_len_i32", "bucket_row_offsets_i32", "row_indices_i32", "bucket_thread_startbit_u32",
-               "bucket_bit_base_i64")
-
-
-def algorithmic_bytes(n, m, art) -> int:
-    """Bytes a decode must move: context bytes + every sidecar tensor once + BF16 output."""
-    return n * m + sum(int(np.asarray(art[k]).nbytes) for k in DECODE_KEYS) + 2 * n * m
 
 
 # ------------------------------------------------------------------------------------------------
@@ -133,7 +163,8 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-# reference arm / CPU baseline: the CPU decode of the same format, all host threads
+# CPU legs: decode by the C port of the decode kernel (the reference has no CPU decoder), encode by the
+# reference's own CPU encoder where it was compiled
 # ------------------------------------------------------------------------------------------------
 
 def cpu_decode_sample(layer, repeats: int):
@@ -152,14 +183,60 @@ def cpu_decode_sample(layer, repeats: int):
     return nbytes / dt / 1e9, dt
 
 
+def _ref_encode_worker(job):
+    """(child process) encode one tensor with the reference's CPU encoder; returns (elements, seconds)."""
+    n, m, seed = job
+    torch.set_num_threads(1)
+    from oracle import ref_encoder as ref
+
+    c = wl.quantize_fp8(wl.random_weight(n, m, seed, "normal"), "channel")
+    t0 = time.perf_counter()
+    ref.build_fp8(c.bf16, c.fp8_u8, c.scales_u16, 7, 1024)
+    return n * m, time.perf_counter() - t0
+
+
+def cpu_encode_baseline(cfg, seed: int) -> dict | None:
+    """The reference's own encoder (kernel/build_huffman.cu:292-969, single-threaded by construction): one
+    thread on two tensors of a layer, then one process per tensor of a whole layer."""
+    from oracle import ref_encoder as ref
+
+    if not ref.available():
+        return None
+    import multiprocessing as mp
+
+    linears = wl.layer_linears(cfg)
+    small = [(n, m, seed + i) for i, (_, n, m) in enumerate(linears[:2])]      # q and k projections
+    e1 = t1 = 0.0
+    for job in small:
+        e, t = _ref_encode_worker(job)
+        e1 += e; t1 += t
+    jobs = [(n, m, seed + i) for i, (_, n, m) in enumerate(linears)]
+    procs = min(len(jobs), os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    with mp.get_context("spawn").Pool(procs) as pool:
+        res = pool.map(_ref_encode_worker, jobs)
+    wall = time.perf_counter() - t0
+    return {"kind": "reference", "what": "kernel/build_huffman.cu huffman_build_fp8_decode_tables_entry, per-channel scales, "
+                                         "max_len=7, threads_per_block=1024",
+            "one_thread": {"value": e1 / t1 / 1e6, "unit": "M elements/s", "cores": 1,
+                           "sample": f"{len(small)} tensors ({e1 / 1e6:.0f} M elements) in {t1:.1f}s"},
+            "processes": {"value": sum(e for e, _ in res) / wall / 1e6, "unit": "M elements/s", "cores": procs,
+                          "sample": f"one decoder layer, {len(jobs)} tensors ({sum(e for e, _ in res) / 1e6:.0f} M elements), one "
+                                    f"process each, {wall:.1f}s wall (process start-up included)"}}
+
+
 def run_reference(args, rank, world):
     from oracle import oracle as orc
 
     if rank != 0:
         return
+    cores = os.cpu_count() or 1
+    orc.set_num_threads(cores)   # not what a launcher exported: torchrun sets OMP_NUM_THREADS=1
+    cores = orc.num_threads()
+    if args.workload != "model":
+        return run_reference_cases(args, cores)
     cfg, tp, wname, layers = workload_for(args.gpus, args.layers)
     layer = encode_layer_cpu(cfg, tp, 0, args.seed)
-    cores = orc.num_threads()
     for _ in range(args.warmup):
         cpu_decode_sample(layer, 1)
     times, nbytes = [], sum(2 * n * m for _, n, m, _, _ in layer)
@@ -168,14 +245,16 @@ def run_reference(args, rank, world):
         times.append(dt)
     ms = 1e3 * float(np.mean(times))
     value = nbytes / (ms / 1e3) / 1e9
-    sample = f"one decoder layer ({len(layer)} tensors, {nbytes / 2 / 1e6:.0f} M elements) per step"
+    sample = (f"one decoder layer of rank 0 ({len(layer)} tensors, {nbytes / 2 / 1e6:.0f} M elements) per step, all host "
+              f"threads of this process; a rate, independent of the GPU count")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "u16", "data": "synthetic",
-        "config": {"workload": f"{wname} fp8-e4m3 per-channel + huffman sidecar (L=7,k=1024), tp={tp}, layers={layers}",
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
+        "config": {"workload": workload_text(wname, tp, layers),
                    "note": "the reference has no CPU decoder; this is the CPU port of its decode kernel "
-                           "(ESC honoured), OpenMP over buckets x sub-streams; bounded sample per step"},
+                           "(ESC honoured), OpenMP over buckets x sub-streams; bounded sample per step",
+                   "cpu": cpu_model()},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -184,7 +263,7 @@ def run_reference(args, rank, world):
 
 
 # ------------------------------------------------------------------------------------------------
-# our arm
+# our arm, whole model
 # ------------------------------------------------------------------------------------------------
 
 def encode_layer_gpu(cfg, tp, rank, seed_base, layer, dev):
@@ -204,26 +283,36 @@ def encode_layer_gpu(cfg, tp, rank, seed_base, layer, dev):
 
 
 def run_ours(args, rank, world, local_rank):
-    from mpserve_b200 import _lib, api, util
+    import MPServe_cuda
+    from mpserve_b200 import _lib, api, shard
 
     _lib.load()  # no fallback: a missing extension is an error
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     cfg, tp, wname, layers = workload_for(args.gpus, args.layers)
-    t_setup = time.perf_counter()
-    model = [encode_layer_gpu(cfg, tp, rank, args.seed, li, dev) for li in range(layers)]
-    torch.cuda.synchronize()
-    n_elem = sum(n * m for layer in model for _, n, m, _, _ in layer)
-    enc_s = time.perf_counter() - t_setup
-    log(f"[rank {rank}] generated, quantised and encoded {layers} layers ({n_elem / 1e9:.2f} G elements) on the GPU "
-        f"in {enc_s:.1f}s")
+    # what a rank holds: compressed inputs (~1.75 B/element) and BF16 outputs; shorten the model rather than
+    # run out of device memory, and say so in config.workload
+    per_layer = sum(wl.tp_shard_shape(nm, n, m, tp)[0] * wl.tp_shard_shape(nm, n, m, tp)[1] for nm, n, m in wl.layer_linears(cfg))
+    budget = 0.85 * torch.cuda.get_device_properties(dev).total_memory - (14 << 30)
+    fit = int(budget // (per_layer * 3.8))
+    if fit < layers:
+        log(f"[rank {rank}] {layers} layers need more than this GPU's memory; running {fit}")
+        layers = max(1, fit)
 
-    # Every layer's compressed inputs are packed into one device buffer with a pinned host twin (what a
-    # loader would hold), so the end-to-end leg moves a layer with one copy; the tensors the decoder
-    # reads are views into the device buffer.
-    entries, layer_entries, layer_bufs = [], [], []
-    alg_bytes = 0
-    for layer in model:
+    # Layer by layer: generate, quantise, encode, pack the compressed inputs into one device buffer (with a
+    # pinned host twin for the end-to-end leg, as a loader would hold them), decode, compare with the source
+    # bit for bit, drop the source.
+    t_setup = time.perf_counter()
+    entries, layer_entries, layer_bufs, shapes = [], [], [], []
+    alg_bytes = n_elem = h2d_bytes = 0
+    want = torch.zeros(2, dtype=torch.int64, device=dev)     # checksum of the source tensors
+    layer0_host = None
+    pinned = 0
+    for li in range(layers):
+        layer = encode_layer_gpu(cfg, tp, rank, args.seed, li, dev)
+        if li == 0 and rank == 0 and world == 1:
+            layer0_host = [(name, n, m, wl.Fp8Case(c.bf16.cpu(), c.fp8_u8.cpu(), c.scales_u16.cpu()),
+                            {k: v.cpu().numpy() for k, v in art.items()}) for name, n, m, c, art in layer]
         arrays = []
         for name, n, m, c, art in layer:
             arrays.append(c.fp8_u8)
@@ -240,42 +329,38 @@ def run_ours(args, rank, world, local_rank):
             views.append(v)
         it = iter(views)
         these = []
-        for item in layer:
-            name, n, m, c, art = item
-            c.fp8_u8 = next(it)
+        for name, n, m, c, art in layer:
+            ctx = next(it)
             d = {k: next(it) for k in DECODE_KEYS}
-            for k in DECODE_KEYS:
-                art[k] = d[k]
-            these.append((c.fp8_u8, d, None))
+            these.append((ctx, d, torch.empty((n, m), dtype=torch.bfloat16, device=dev)))
             alg_bytes += n * m + sum(v.numel() * v.element_size() for v in d.values()) + 2 * n * m
+            n_elem += n * m
+            shapes.append((n, m))
+        lp = api.BucketDecodePlan(these, mode=0)
+        lp.decode()
+        for (name, n, m, c, art), (_, _, out) in zip(layer, these):
+            assert torch.equal(out.view(torch.uint16), c.bf16.view(torch.uint16)), f"decode mismatch in layer {li} {name}"
+            api.checksum_u16(c.bf16, want)
+        host = None
+        if pinned + total <= E2E_MAX_PINNED_BYTES:
+            host = torch.empty(total, dtype=torch.uint8, pin_memory=True)
+            host.copy_(flat)
+            pinned += total
+            h2d_bytes += total
         entries.extend(these)
-        layer_entries.append(these)
-        layer_bufs.append((flat, flat.cpu().pin_memory()))
-        del arrays, views
-    torch.cuda.empty_cache()
-    h2d_bytes = sum(f.numel() for f, _ in layer_bufs)
-
-    plan = api.BucketDecodePlan(entries, mode=0)
-    out_bytes = sum(o.numel() * 2 for o in plan.outputs)
-    elements = out_bytes // 2
+        layer_entries.append((these, lp))
+        layer_bufs.append((flat, host))
+        del layer, arrays, views
     torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    enc_s = time.perf_counter() - t_setup
+    log(f"[rank {rank}] generated, quantised, encoded and verified {layers} layers ({n_elem / 1e9:.2f} G elements) in {enc_s:.1f}s")
 
-    # correctness of what is about to be timed: every decoded tensor against its source, bit for bit
+    plan = api.BucketDecodePlan(entries, mode=0)     # the whole model in one launch, same buffers and outputs
+    out_bytes = 2 * n_elem
     plan.decode()
     torch.cuda.synchronize()
-    want_sum = 0
-    idx = 0
-    for layer in model:
-        for _, n, m, c, _ in layer:
-            assert torch.equal(plan.outputs[idx].view(torch.uint16), c.bf16.view(torch.uint16)), "decode mismatch"
-            want_sum += int(c.bf16.view(torch.uint16).to(torch.int64).sum())
-            idx += 1
-    want_sum %= (1 << 64)
-    layer0_host = [(name, n, m, wl.Fp8Case(c.bf16.cpu(), c.fp8_u8.cpu(), c.scales_u16.cpu()),
-                    {k: v.cpu().numpy() for k, v in art.items()}) for name, n, m, c, art in model[0]]
-    for layer in model:          # the sources are no longer needed on the device
-        for item in layer:
-            item[3].bf16 = None
+    assert not api.decode_timed_out(dev), "a bounded wait ran out in the verification decode"
 
     use_dist = world > 1
     if use_dist:
@@ -318,6 +403,7 @@ def run_ours(args, rank, world, local_rank):
     roll(0.3)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
+    assert not api.decode_timed_out(dev), "a bounded wait ran out in the timed region"
     total_ms = t_begin.elapsed_time(t_end)
     kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
     t = torch.tensor([total_ms, kernel_ms], dtype=torch.float64, device=dev)
@@ -326,15 +412,44 @@ def run_ours(args, rank, world, local_rank):
     total_ms, kernel_ms_max = float(t[0]), float(t[1])
     ms_per_step = total_ms / args.steps
 
+    # ---- the same step through the drop-in per-tensor entry: one call per weight, a fresh tensor each -------
+    dropin = None
+    if not args.no_dropin:
+        calls = [(ctx, [d[k] for k in DECODE_KEYS], n, m) for (ctx, d, _), (n, m) in zip(entries, shapes)]
+
+        def dropin_step():
+            outs = None
+            for ctx, a, n, m in calls:
+                outs = MPServe_cuda.huffman_decode_fp8(ctx, *a, n, m, 7)   # the previous result is released, as in a forward
+            return outs
+
+        for _ in range(2):
+            dropin_step()
+        barrier()
+        d_steps = max(1, min(args.steps, 5))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.perf_counter()
+        e0.record()
+        for _ in range(d_steps):
+            dropin_step()
+        e1.record()
+        host_issue_ms = 1e3 * (time.perf_counter() - w0) / d_steps
+        barrier()
+        d_ms = e0.elapsed_time(e1) / d_steps
+        t = torch.tensor([d_ms], dtype=torch.float64, device=dev)
+        if use_dist:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        d_ms = float(t[0])
+        dropin = {"value": world * out_bytes / (d_ms / 1e3) / 1e9, "unit": UNIT, "ms_per_step": d_ms,
+                  "calls_per_step": len(calls), "host_issue_ms_per_step": host_issue_ms, "steps": d_steps,
+                  "how": "MPServe_cuda.huffman_decode_fp8 once per weight, inputs resident, a newly allocated output per "
+                         "call (kernel/wrapper.cpp:457-503 semantics), device time of the whole step"}
+
     # ---- end to end: pinned host -> device copy of the compressed inputs, decode, checksum back ------
-    # One plan per layer over the same buffers and outputs: layer i is decoded (and check-summed) on the
-    # compute stream while layer i+1 crosses PCIe on the copy stream.
-    idx = 0
-    layer_plans = []
-    for these in layer_entries:
-        with_out = [(ctx, d, plan.outputs[idx + j]) for j, (ctx, d, _) in enumerate(these)]
-        layer_plans.append(api.BucketDecodePlan(with_out, mode=0))
-        idx += len(these)
+    # Layer i is decoded (and check-summed) on the compute stream while layer i+1 crosses PCIe on the copy
+    # stream.  Layers whose inputs did not fit the pinned-memory allowance are left out of this leg.
+    e2e_layers = [(flat, host, lp, these) for (flat, host), (these, lp) in zip(layer_bufs, layer_entries) if host is not None]
+    e2e_out_bytes = sum(2 * o.numel() for _, _, _, these in e2e_layers for _, _, o in these)
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream(dev)
     acc = torch.zeros(2, dtype=torch.int64, device=dev)
@@ -343,7 +458,7 @@ def run_ours(args, rank, world, local_rank):
     def e2e_step():
         acc.zero_()
         copy_stream.wait_stream(main_stream)   # the previous step's decodes have read the buffers
-        for (flat_dev, flat_host), lp in zip(layer_bufs, layer_plans):
+        for flat_dev, flat_host, lp, these in e2e_layers:
             with torch.cuda.stream(copy_stream):
                 flat_dev.copy_(flat_host, non_blocking=True)
                 ev = torch.cuda.Event()
@@ -356,76 +471,323 @@ def run_ours(args, rank, world, local_rank):
     e2e_step()
     torch.cuda.synchronize()
     barrier()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
-        acc_host = e2e_step()
+        e2e_step()
     e1.record()
     barrier()
+    assert not api.decode_timed_out(dev), "a bounded wait ran out in the end-to-end leg"
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
     if use_dist:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t[0])
-    e2e_launches = e2e_steps * (len(layer_plans) + len(entries))
+    e2e_launches = e2e_steps * sum(1 + len(these) for _, _, _, these in e2e_layers)
 
-    # ---- checksum of all ranks' outputs over NCCL (outside every timed region) -------------------------
-    got_sum = int(acc_host[0]) % (1 << 64)
-    assert got_sum == want_sum, f"checksum mismatch on rank {rank}: {got_sum} != {want_sum}"
-    if use_dist:
-        pair = torch.tensor([got_sum % (1 << 62), want_sum % (1 << 62)], dtype=torch.int64, device=dev)
-        dist.all_reduce(pair, op=dist.ReduceOp.SUM)
-        assert int(pair[0]) == int(pair[1]), "all-reduced checksum mismatch"
+    # ---- checksum of all ranks' outputs (outside every timed region; NCCL when there are several ranks) ----
+    got = torch.zeros(2, dtype=torch.int64, device=dev)
+    for _, _, o in entries:
+        api.checksum_u16(o, got)
+    got_host, want_host = got.cpu(), want.cpu()
+    mine = (int(got_host[0]) & shard.MASK64, int(got_host[1]) & shard.MASK64)
+    expect = (int(want_host[0]) & shard.MASK64, int(want_host[1]) & shard.MASK64)
+    assert mine == expect, f"checksum mismatch on rank {rank}: {mine} != {expect}"
+    all_got = shard.all_reduce_checksum(mine, device=dev)
+    all_want = shard.all_reduce_checksum(expect, device=dev)
+    assert all_got == all_want, "all-reduced checksum mismatch"
 
     if rank != 0:
         return
-    peaks_path = ROOT / "MEASURED_PEAKS.json"
-    if peaks_path.exists():
-        peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    else:
-        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    peak, peak_src = hbm_peak()
     achieved = alg_bytes / (kernel_ms_max / 1e3) / 1e9
     value = world * out_bytes / (ms_per_step / 1e3) / 1e9
-    e2e_value = world * out_bytes / (e2e_ms / 1e3) / 1e9
+    e2e_value = world * e2e_out_bytes / (e2e_ms / 1e3) / 1e9
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
         from oracle import oracle as orc
 
+        orc.set_num_threads(os.cpu_count() or 1)
         cores = orc.num_threads()
         cpu_decode_sample(layer0_host, 1)
         one, dt1 = cpu_decode_sample(layer0_host, 1)
         reps = int(max(1, min(200, 12.0 / max(dt1, 1e-3))))   # about 12 s of CPU work
         gbs, dt = cpu_decode_sample(layer0_host, reps)
-        cpu_baseline = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port",
+        cpu_baseline = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "cpu": cpu_model(),
                         "sample": f"one decoder layer ({len(layer0_host)} tensors) decoded {reps}x in {dt:.1f}s by the CPU "
-                                  f"port of the reference decode kernel, OpenMP, {cores} threads"}
+                                  f"port of the reference decode kernel, OpenMP, {cores} threads",
+                        "encode": cpu_encode_baseline(cfg, args.seed),
+                        "encode_gpu": {"value": n_elem / enc_s / 1e6, "unit": "M elements/s",
+                                       "what": "this library's builder on the GPU, weight generation, quantisation, packing "
+                                               "and verification included"}}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "u16", "data": "synthetic",
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
+        "vs_baseline": None, "dtype": "u16", "data": "synthetic",
         "config": {
-            "workload": f"{wname} fp8-e4m3 per-channel + huffman sidecar (L=7,k=1024), tp={tp}, layers={layers}",
-            "tensors_per_rank": len(entries), "elements_per_rank": elements,
+            "workload": workload_text(wname, tp, layers),
+            "tensors_per_rank": len(entries), "elements_per_rank": n_elem,
             "l2": "inputs+outputs per step far exceed L2 (no flush needed)",
-            "inputs": "every layer random-init with its own seed, quantised and encoded on the GPU by this library's "
-                      f"builder ({n_elem / enc_s / 1e6:.0f} M elements/s including weight generation)",
+            "inputs": "every layer random-init with its own seed, quantised and encoded on the GPU by this library's builder",
             "decode": f"one launch per step, threads={plan.threads}, chains={plan.chains}",
         },
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_ELEMENT * elements,
-                     "traffic_source": "ncu capture of a 218 M-element launch, scaled by elements", "peak_source": peak_src, "algorithmic_bytes_per_launch": alg_bytes,
-                     "kernel_ms": kernel_ms_max},
+                     "traffic": NCU_TRAFFIC_BYTES_PER_ELEMENT * n_elem,
+                     "traffic_source": "ncu capture of a smaller launch, scaled by elements", "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": kernel_ms_max},
         "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 16,
-                "ms_per_step": e2e_ms, "steps": e2e_steps, "gpu_launches": e2e_launches,
+                "ms_per_step": e2e_ms, "steps": e2e_steps, "gpu_launches": e2e_launches, "layers": len(e2e_layers),
                 "how": "per layer: one pinned-host -> device copy of its packed compressed inputs on a copy stream, "
-                       "then one decode launch and the checksums on the compute stream; 16 bytes read back per step"},
+                       "then one decode launch and the checksums on the compute stream; 16 bytes read back per step"
+                       + ("" if len(e2e_layers) == layers else
+                          f"; {len(e2e_layers)} of {layers} layers (pinned-memory allowance), a rate over those")},
+        "dropin": dropin,
         "gpu_launches": args.steps,
         "clocks": clocks,
     }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# single tensors through the per-tensor entry points (configs 1, 3, 4)
+# ------------------------------------------------------------------------------------------------
+
+def _time_calls(fn, flush, reps: int):
+    """(median, best) milliseconds of fn() with a cold L2."""
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(reps):
+        flush.fill_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2], times[0]
+
+
+def _e2e_call(inputs_dev, run, out_of, reps: int):
+    """Milliseconds of: copy every compressed input from pinned host memory, decode, checksum, read 16 bytes back."""
+    from mpserve_b200 import api
+
+    hosts = [t.cpu().pin_memory() for t in inputs_dev]
+    acc = torch.zeros(2, dtype=torch.int64, device=inputs_dev[0].device)
+
+    def step():
+        acc.zero_()
+        for d, h in zip(inputs_dev, hosts):
+            d.copy_(h, non_blocking=True)
+        api.checksum_u16(out_of(run()), acc)
+        return acc.cpu()
+
+    step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps, sum(h.numel() * h.element_size() for h in hosts)
+
+
+def _case_result(label, n, m, art, keys, ctx_bytes, med, best, e2e_ms, h2d, host_us):
+    elems = n * m
+    alg = ctx_bytes + sum(art[k].numel() * art[k].element_size() for k in keys) + 2 * elems
+    return {"case": label, "elements": elems, "ms_median": med, "ms_best": best, "bf16_gbps": 2 * elems / med / 1e6,
+            "algorithmic_bytes": alg, "algorithmic_gbps": alg / med / 1e6, "e2e_ms": e2e_ms, "h2d_bytes": h2d,
+            "host_us_per_call": host_us, "code_bits_per_element": 64.0 * art["bitstream_u64"].numel() / elems}
+
+
+def _host_us(fn, reps=50):
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        fn()
+    dt = time.perf_counter() - t0
+    torch.cuda.synchronize()
+    return 1e6 * dt / reps
+
+
+def fp8_case(n, m, dist, scale_mode, k, seed, dev, flush, reps):
+    import MPServe_cuda
+
+    c = wl.quantize_fp8(wl.random_weight(n, m, seed, dist, device=dev), scale_mode)
+    art = MPServe_cuda.huffman_build_fp8_decode_tables(c.bf16, c.fp8_u8, c.scales_u16, max_len=7, threads_per_block=k)
+    a = [art[key] for key in DECODE_KEYS]
+
+    def run():
+        return MPServe_cuda.huffman_decode_fp8(c.fp8_u8, *a, n, m, 7)
+
+    out = run()
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.uint16), c.bf16.view(torch.uint16)), "decode mismatch"
+    med, best = _time_calls(run, flush, reps)
+    e2e_ms, h2d = _e2e_call([c.fp8_u8] + a, run, lambda o: o, max(3, reps // 3))
+    r = _case_result(f"fp8 {scale_mode} {dist} {n}x{m} k={k}", n, m, art, DECODE_KEYS, n * m, med, best, e2e_ms, h2d,
+                     _host_us(run))
+    r.update(buckets=int(art["bucket_table_i32"].size(0)), tables=int(art["decode_syms_u16"].size(0)))
+    return r, (c, art)
+
+
+def awq_case(name, n, m, layout, k, seed, dev, flush, reps):
+    import MPServe_cuda
+
+    c = wl.quantize_awq(wl.random_weight(n, m, seed, "normal", device=dev), 128)
+    if layout == "bucket":
+        art = MPServe_cuda.huffman_build_awq_int4_bucket_decode_tables(c.bf16, c.int4_u8, c.scales_u16, max_len=11,
+                                                                       threads_per_block=k)
+        keys = DECODE_KEYS
+        a = [art[key] for key in keys]
+
+        def run():
+            return MPServe_cuda.huffman_decode_awq_int4_bucket(c.int4_u8, *a, n, m, 11)
+    elif layout == "shared":
+        art = MPServe_cuda.huffman_build_awq_decode_tables(c.bf16, c.int4_u8, c.scales_u16, max_len=11)
+        keys = SHARED_KEYS
+        a = [art[key] for key in keys]
+
+        def run():
+            return MPServe_cuda.huffman_decode_awq_shared_table(*a, n * m, 11).view(torch.bfloat16).view(n, m)
+    else:
+        art = MPServe_cuda.huffman_build_awq_int4_bucket_decode_tables_by_scale(c.bf16, c.int4_u8, c.scales_u16, max_len=11,
+                                                                                threads=k, group_cap=1024)
+        keys = BYSCALE_KEYS
+        a = [art[key] for key in keys]
+        gs = int(art["shape_nmkg_i64"][3])
+
+        def run():
+            return MPServe_cuda.huffman_decode_awq_int4_bucket_by_scale(c.int4_u8, *a, n, m, 11, gs)
+
+    out = run()
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.uint16), c.bf16.view(torch.uint16)), "decode mismatch"
+    med, best = _time_calls(run, flush, reps)
+    inputs = a if layout == "shared" else [c.int4_u8] + a      # the shared layout reads no int4 codes
+    e2e_ms, h2d = _e2e_call(inputs, run, lambda o: o, max(2, reps // 5))
+    r = _case_result(f"awq g128 {layout} {name} {n}x{m} k={k}", n, m, art, keys, 0 if layout == "shared" else n * m, med,
+                     best, e2e_ms, h2d, _host_us(run, 20))
+    return r, None
+
+
+def case_list(args):
+    """(label of the workload, list of case constructors) for --workload single | sizes | awq."""
+    k = args.k
+    if args.workload == "single":
+        ks = [k] if k else [1024, 256]
+        return ("single linear weight 4096x4096, N(0,0.02), per-tensor FP8-E4M3 scale, huffman sidecar (L=7), one "
+                "MPServe_cuda.huffman_decode_fp8 call",
+                [("fp8", dict(n=4096, m=4096, dist="normal", scale_mode="tensor", k=kk, seed=7)) for kk in ks])
+    if args.workload == "sizes":
+        cases = []
+        for dist in ("normal", "student_t"):
+            for n, m in SIZES:
+                if 2 * n * m <= args.max_bytes:
+                    cases.append(("fp8", dict(n=n, m=m, dist=dist, scale_mode="channel", k=k or 1024, seed=11)))
+        return ("single tensors of 64 KB ... 1 GB of BF16, N(0,0.02) and Student-t(4)x0.02, per-channel FP8-E4M3 scales, "
+                "huffman sidecar (L=7,k=1024), one call per tensor", cases)
+    cases = []
+    for layout in ("byscale", "bucket", "shared"):
+        for i, (name, n, m) in enumerate(wl.layer_linears(wl.LLAMA3_8B)):
+            if layout == "shared" and i not in (0, 1):
+                continue   # one square and one small tensor: the format's metadata is ~20 B per element
+            cases.append(("awq", dict(name=name, n=n, m=m, layout=layout, k=k or 256, seed=100 + i)))
+    return ("llama3-8b-shaped linears as INT4 AWQ (group 128, fp16 scales), huffman sidecar (L=11) in the by-scale, "
+            "rectangular and shared-table layouts, one call per tensor", cases)
+
+
+def run_cases(args, local_rank):
+    from mpserve_b200 import _lib, api
+
+    _lib.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    label, cases = case_list(args)
+    reps = max(5, args.steps)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    rows, first = [], None
+    for kind, kw in cases:
+        r, keep = (fp8_case if kind == "fp8" else awq_case)(dev=dev, flush=flush, reps=reps, **kw)
+        rows.append(r)
+        if first is None:
+            first = keep
+        log(json.dumps(r))
+        torch.cuda.empty_cache()
+    clocks = sampler.stop()
+    assert not api.decode_timed_out(dev), "a bounded wait ran out"
+    peak, peak_src = hbm_peak()
+    head = rows[0]     # the line's headline is its first case; every case is listed under "cases"
+    cpu_baseline = None
+    if not args.no_cpu_baseline and first is not None:
+        from oracle import oracle as orc
+
+        orc.set_num_threads(os.cpu_count() or 1)
+        c, art = first
+        n, m = int(c.fp8_u8.shape[0]), int(c.fp8_u8.shape[1])
+        host = [("t", n, m, wl.Fp8Case(c.bf16.cpu(), c.fp8_u8.cpu(), c.scales_u16.cpu()),
+                 {key: v.cpu().numpy() for key, v in art.items()})]
+        cpu_decode_sample(host, 1)
+        _, dt1 = cpu_decode_sample(host, 1)
+        reps_cpu = int(max(1, min(500, 10.0 / max(dt1, 1e-3))))
+        gbs, dt = cpu_decode_sample(host, reps_cpu)
+        cpu_baseline = {"value": gbs, "unit": UNIT, "cores": orc.num_threads(), "kind": "port", "cpu": cpu_model(),
+                        "sample": f"{head['case']} decoded {reps_cpu}x in {dt:.1f}s by the CPU port of the reference decode "
+                                  "kernel, OpenMP"}
+    line = {
+        "metric": METRIC, "value": head["bf16_gbps"], "unit": UNIT, "n_gpus": 1, "steps": reps, "warmup": 3,
+        "ms_per_step": head["ms_median"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u16", "data": "synthetic",
+        "config": {"workload": label, "headline_case": head["case"],
+                   "l2": "a 256 MB buffer is written before every timed call"},
+        "roofline": {"bound": "hbm", "achieved": head["algorithmic_gbps"], "peak": peak, "unit": "GB/s",
+                     "frac": head["algorithmic_gbps"] / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": head["algorithmic_bytes"], "kernel_ms": head["ms_median"]},
+        "cpu_baseline": cpu_baseline,
+        "e2e": {"value": 2 * head["elements"] / head["e2e_ms"] / 1e6, "unit": UNIT, "h2d_bytes_per_step": head["h2d_bytes"],
+                "d2h_bytes_per_step": 16, "ms_per_step": head["e2e_ms"],
+                "how": "per call: every compressed input copied from pinned host memory, one decode call, checksum, 16 "
+                       "bytes read back"},
+        "gpu_launches": reps,
+        "cases": rows,
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_reference_cases(args, cores):
+    """CPU port on the first case of the workload (FP8 workloads), a bounded number of repetitions per step."""
+    from oracle import oracle as orc
+
+    label, cases = case_list(args)
+    kind, kw = cases[0]
+    if kind != "fp8":
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm times the FP8 decode port only"}), flush=True)
+        return
+    n, m = kw["n"], kw["m"]
+    c = wl.quantize_fp8(wl.random_weight(n, m, kw["seed"], kw["dist"]), kw["scale_mode"])
+    art = orc.build_fp8(c.bf16.view(torch.uint16).numpy(), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, kw["k"])
+    layer = [("t", n, m, c, art)]
+    for _ in range(args.warmup):
+        cpu_decode_sample(layer, 1)
+    times = [cpu_decode_sample(layer, 1)[1] for _ in range(args.steps)]
+    ms = 1e3 * float(np.mean(times))
+    value = 2 * n * m / (ms / 1e3) / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u16", "data": "synthetic",
+            "config": {"workload": label, "headline_case": f"fp8 {kw['scale_mode']} {kw['dist']} {n}x{m} k={kw['k']}",
+                       "cpu": cpu_model()},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": "the headline case once per step, all host threads"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
@@ -435,9 +797,13 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=None, help="override the layer count (smaller = quicker)")
+    ap.add_argument("--workload", default="model", choices=["model", "single", "sizes", "awq"])
+    ap.add_argument("--layers", type=int, default=None, help="shorten the model to this many layers (quicker)")
+    ap.add_argument("--k", type=int, default=None, help="sub-streams per bucket for the single-tensor workloads")
+    ap.add_argument("--max-bytes", type=int, default=1 << 30, help="largest BF16 output of --workload sizes")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-dropin", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)  # timing hygiene: never fewer than three warm-up steps
 
@@ -446,6 +812,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload != "model":
+        if rank == 0:
+            run_cases(args, local_rank)
         return
     if world > 1:
         import torch.distributed as dist

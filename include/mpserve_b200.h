@@ -51,8 +51,10 @@ MPS_API size_t mps_workspace_bytes(void);
 
 /* Every wait inside the decode kernels is bounded; a kernel whose wait ran out stops taking work and
  * records it in the workspace.  This call waits for the stream, reports whether any launch since the
- * last query gave up (*timed_out = 1; its outputs are then incomplete) and clears the record.  The
- * reference has no counterpart: its kernels have no waits. */
+ * last query gave up (*timed_out = 1; its outputs are then incomplete) and clears the record.
+ * workspace == NULL asks about the library's own scratch, i.e. about mps_decode_fp8_noalloc calls (that
+ * entry keeps the record across calls until it is read here).  The reference has no counterpart: its
+ * kernels have no waits. */
 MPS_API int mps_decode_status(void* workspace, size_t workspace_bytes, void* stream, int32_t* timed_out);
 
 /* One compressed tensor (all pointers device) ---------------------------------------------------
@@ -174,6 +176,16 @@ MPS_API int mps_decode_bucket_tensor(const mps_bucket_tensor* tensor_host, void*
 MPS_API int mps_decode_bucket_batch(const mps_bucket_tensor* tensors_dev, const int64_t* item_prefix_dev, int count,
                             int64_t total_items, int32_t threads, int32_t chains, int32_t mode,
                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* Self-test of the bounded waits, for bring-up on a new machine and for the test-suite; no counterpart in
+ * the reference.  Decodes one tensor (through the persistent kernel, whatever its size) with the context
+ * bytes of ONE block of steps deliberately never copied: block `stall_block` (0-based, counted per CTA) is
+ * announced to the decoding warps but its bytes do not come.  Their wait gives up after `polls` polls,
+ * the CTA stops taking work, waits (bounded again) for the copies it still has in flight and returns;
+ * mps_decode_status then reports 1.  Nothing hangs or faults; the output is incomplete by design. */
+MPS_API int mps_selftest_stalled_decode(const mps_bucket_tensor* tensor_host, int32_t stall_block, uint32_t polls,
+                                        void* workspace, size_t workspace_bytes, void* stream);
+
 
 /* Sidecar builder -------------------------------------------------------------------------------
  * Together these replace huffman_cpp::huffman_build_fp8_decode_tables_entry

@@ -51,6 +51,7 @@ _PROTOS = {
     "mps_decode_bucket_batch": (C.c_int, [_p, _p, C.c_int, _i64, _i32, _i32, _i32, _p, C.c_size_t, _p]),
     "mps_decode_bucket_tensor": (C.c_int, [C.POINTER(BucketTensor), _p, C.c_size_t, _p]),
     "mps_decode_status": (C.c_int, [_p, C.c_size_t, _p, C.POINTER(_i32)]),
+    "mps_selftest_stalled_decode": (C.c_int, [C.POINTER(BucketTensor), _i32, C.c_uint32, _p, C.c_size_t, _p]),
     "mps_checksum_u16": (C.c_int, [_p, _i64, _p, _p]),
     "mps_build_workspace_bytes": (C.c_size_t, [_i64, _i64]),
     "mps_build_analyze": (C.c_int, [_p, _p, _p, _p, _i32, _i64, _i64, _i64, _i64, _i64, _i32, _i64, _p, C.c_size_t, _p,

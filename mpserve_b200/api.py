@@ -22,7 +22,7 @@ __all__ = [
     "huffman_decode_awq_int4_bucket_by_scale", "huffman_decode_awq_shared_table",
     "huffman_build_fp8_decode_tables", "huffman_build_awq_int4_bucket_decode_tables",
     "huffman_build_awq_int4_bucket_decode_tables_by_scale", "huffman_build_awq_decode_tables",
-    "BucketDecodePlan", "checksum_u16", "decode_timed_out",
+    "BucketDecodePlan", "checksum_u16", "decode_timed_out", "noalloc_decode_timed_out", "selftest_stalled_decode",
 ]
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
@@ -70,6 +70,43 @@ def decode_timed_out(device: torch.device | None = None) -> bool:
         flag = C.c_int32(0)
         _lib.check(_lib.load().mps_decode_status(ws.data_ptr(), ws.numel() * 4, _stream_ptr(dev), C.byref(flag)))
     return bool(flag.value)
+
+
+def noalloc_decode_timed_out(device: torch.device | None = None) -> bool:
+    """Same question for the decodes made through ``mps_decode_fp8_noalloc``, whose queue counters (and
+    give-up record) live in the library's own device scratch instead of a caller's workspace."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        flag = C.c_int32(0)
+        _lib.check(_lib.load().mps_decode_status(None, 0, _stream_ptr(dev), C.byref(flag)))
+    return bool(flag.value)
+
+
+def selftest_stalled_decode(ctx_u8: torch.Tensor, art: dict, out: torch.Tensor, stall_block: int = 1,
+                            polls: int = 20000) -> None:
+    """Bring-up check of the bounded waits (``mps_selftest_stalled_decode``): decodes one FP8 tensor with the
+    context bytes of one block of steps never copied, so that the decoding warps' wait runs out after
+    ``polls`` polls and the kernel returns early.  ``decode_timed_out()`` is True afterwards; ``out`` is
+    incomplete.  Nothing hangs or faults."""
+    dev = ctx_u8.device
+    d = _lib.BucketTensor()
+    n, m = int(ctx_u8.shape[0]), int(ctx_u8.shape[1])
+    d.ctx_bytes = ctx_u8.data_ptr()
+    d.bitstream = art["bitstream_u64"].data_ptr(); d.bitstream_words = art["bitstream_u64"].numel()
+    d.decode_syms = art["decode_syms_u16"].data_ptr(); d.decode_lens = art["decode_lens_u8"].data_ptr()
+    d.num_tables = art["decode_syms_u16"].size(0)
+    d.bucket_table = art["bucket_table_i32"].data_ptr()
+    d.bucket_col_start = art["bucket_col_start_i32"].data_ptr(); d.bucket_col_len = art["bucket_col_len_i32"].data_ptr()
+    d.bucket_row_offsets = art["bucket_row_offsets_i32"].data_ptr(); d.row_indices = art["row_indices_i32"].data_ptr()
+    d.num_rows = art["row_indices_i32"].numel()
+    d.thread_startbit = art["bucket_thread_startbit_u32"].data_ptr(); d.bucket_bit_base = art["bucket_bit_base_i64"].data_ptr()
+    d.num_buckets = art["bucket_table_i32"].size(0)
+    d.k = int(art["bucket_thread_startbit_u32"].size(1)) - 1
+    d.mode, d.n, d.m, d.out = 0, n, m, out.data_ptr()
+    with torch.cuda.device(dev):
+        ws = _workspace(dev)
+        _lib.check(_lib.load().mps_selftest_stalled_decode(C.byref(d), int(stall_block), int(polls), ws.data_ptr(),
+                                                          ws.numel() * 4, _stream_ptr(dev)))
 
 
 def cuda_clock_rate_khz() -> int:
@@ -135,14 +172,12 @@ def _check_rect(bucket_col_start_i32, bucket_col_len_i32, bucket_row_offsets_i32
     return k
 
 
-def huffman_decode_fp8(fp8_params_u8, bitstream_u64, decode_syms_u16, decode_lens_u8, bucket_table_i32,
-                       bucket_col_start_i32, bucket_col_len_i32, bucket_row_offsets_i32, row_indices_i32,
-                       bucket_thread_startbit_u32, bucket_bit_base_i64, n, m, max_len=12):
-    """FP8 + sidecar -> BF16 ``[n, m]`` (kernel/wrapper.cpp:457-503, decode_huffman.cu:591-758).
-
-    Launches asynchronously on the current CUDA stream of the inputs' device and returns a newly
-    allocated tensor, as the reference does.
-    """
+def validate_decode_fp8(fp8_params_u8, bitstream_u64, decode_syms_u16, decode_lens_u8, bucket_table_i32,
+                        bucket_col_start_i32, bucket_col_len_i32, bucket_row_offsets_i32, row_indices_i32,
+                        bucket_thread_startbit_u32, bucket_bit_base_i64, n, m, max_len, require_cuda: bool = True):
+    """Argument checks of ``huffman_decode_fp8`` in the order, and with the messages, of the reference
+    entry (decode_huffman.cu:606-697).  Returns ``(n, m, max_len, B, k, tensors)``.  ``require_cuda=False``
+    leaves out the device test only, so that the host-side contract can be exercised without a GPU."""
     names = ("fp8_params_u8", "bitstream_u64", "decode_syms_u16", "decode_lens_u8", "bucket_table_i32",
              "bucket_col_start_i32", "bucket_col_len_i32", "bucket_row_offsets_i32", "row_indices_i32",
              "bucket_thread_startbit_u32", "bucket_bit_base_i64")
@@ -150,7 +185,13 @@ def huffman_decode_fp8(fp8_params_u8, bitstream_u64, decode_syms_u16, decode_len
                bucket_col_start_i32, bucket_col_len_i32, bucket_row_offsets_i32, row_indices_i32,
                bucket_thread_startbit_u32, bucket_bit_base_i64)
     for t, nm in zip(tensors, names):
-        _check_cuda_contig(t, nm)
+        if require_cuda:
+            _check_cuda_contig(t, nm)
+        else:
+            if not isinstance(t, torch.Tensor):
+                raise ValueError(f"{nm} must be defined")
+            if not t.is_contiguous():
+                raise ValueError(f"{nm} must be contiguous")
     _check_bucket_common(fp8_params_u8, bitstream_u64, decode_syms_u16, decode_lens_u8, bucket_table_i32,
                          bucket_thread_startbit_u32, bucket_bit_base_i64, "fp8_params_u8", 256)
     n, m, max_len = int(n), int(m), int(max_len)
@@ -166,8 +207,30 @@ def huffman_decode_fp8(fp8_params_u8, bitstream_u64, decode_syms_u16, decode_len
     k = _check_rect(bucket_col_start_i32, bucket_col_len_i32, bucket_row_offsets_i32, row_indices_i32,
                     bucket_thread_startbit_u32, bucket_bit_base_i64, B)
     _check_tables(decode_syms_u16, decode_lens_u8, 7)
+    return n, m, max_len, B, k, tensors
+
+
+def huffman_decode_fp8(fp8_params_u8, bitstream_u64, decode_syms_u16, decode_lens_u8, bucket_table_i32,
+                       bucket_col_start_i32, bucket_col_len_i32, bucket_row_offsets_i32, row_indices_i32,
+                       bucket_thread_startbit_u32, bucket_bit_base_i64, n, m, max_len=12, *, out=None):
+    """FP8 + sidecar -> BF16 ``[n, m]`` (kernel/wrapper.cpp:457-503, decode_huffman.cu:591-758).
+
+    Launches asynchronously on the current CUDA stream of the inputs' device and returns a newly
+    allocated tensor, as the reference does.  ``out`` (keyword only, not part of the reference's
+    signature) names a contiguous BF16 ``[n, m]`` tensor to decode into instead: a row range of a fused
+    ``qkv`` / ``gate_up`` weight, or a buffer kept across forwards.
+    """
+    n, m, max_len, B, k, tensors = validate_decode_fp8(
+        fp8_params_u8, bitstream_u64, decode_syms_u16, decode_lens_u8, bucket_table_i32, bucket_col_start_i32,
+        bucket_col_len_i32, bucket_row_offsets_i32, row_indices_i32, bucket_thread_startbit_u32,
+        bucket_bit_base_i64, n, m, max_len)
     dev = _same_device(tensors)
-    out = torch.empty((n, m), dtype=torch.bfloat16, device=dev)
+    if out is None:
+        out = torch.empty((n, m), dtype=torch.bfloat16, device=dev)
+    else:
+        _check_cuda_contig(out, "out")
+        if out.dtype != torch.bfloat16 or out.numel() != n * m or out.device != dev:
+            raise ValueError("out must be a contiguous bfloat16 CUDA tensor of n*m elements on the inputs' device")
     with torch.cuda.device(dev):
         ws = _workspace(dev)
         rc = _lib.load().mps_decode_fp8(
@@ -401,6 +464,10 @@ class BucketDecodePlan:
             n, m = int(ctx.shape[0]), int(ctx.shape[1])
             if out is None:
                 out = torch.empty((n, m), dtype=torch.bfloat16, device=self.device)
+            elif (not out.is_cuda or out.device != self.device or not out.is_contiguous() or out.element_size() != 2
+                  or out.numel() != n * m):
+                raise ValueError("an output must be a contiguous 16-bit CUDA tensor of n*m elements on the plan's device "
+                                 "(a row range of a larger row-major tensor qualifies)")
             outs[j] = out
             self._keep.append((ctx, art))
             d = descs[i]

@@ -92,6 +92,15 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* Threads of the decode loops from now on (a launcher may have exported OMP_NUM_THREADS=1). */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* Length-limited code lengths (package-merge), build_huffman.cu:46-118                        */
 /*                                                                                             */

@@ -70,8 +70,9 @@ def num_threads() -> int:
 
 
 def set_num_threads(n: int) -> None:
-    """OpenMP reads OMP_NUM_THREADS at first use; call before the first decode."""
-    os.environ["OMP_NUM_THREADS"] = str(int(n))
+    """Threads of the decode loops from now on, whatever OMP_NUM_THREADS said when the OpenMP runtime
+    started (torchrun exports OMP_NUM_THREADS=1 to its ranks)."""
+    lib().orc_set_num_threads(C.c_int(int(n)))
 
 
 def _ptr(a: np.ndarray):

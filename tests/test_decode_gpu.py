@@ -160,6 +160,28 @@ def test_no_bounded_wait_runs_out_in_normal_operation(dev):
     assert api.decode_timed_out(dev) is False
 
 
+def test_bounded_wait_runs_out_and_is_reported(dev):
+    """The give-up path, made to happen on the host's request and without any fault: the producer leaves the
+    context bytes of one block out (mps_selftest_stalled_decode), the decoding warps' wait runs out after a
+    few thousand polls, the kernel stops taking work, drains what it has in flight and returns; the status
+    call says so once, and the very next decode on the same workspace is bit-exact."""
+    n, m = 1024, 4096
+    c = wl.quantize_fp8(wl.random_weight(n, m, 77, "normal"), "tensor")
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
+    d = util.artifacts_to_device(art, dev)
+    ctx = c.fp8_u8.to(dev)
+    assert api.decode_timed_out(dev) is False
+    out = torch.zeros((n, m), dtype=torch.bfloat16, device=dev)
+    api.selftest_stalled_decode(ctx, d, out, stall_block=1, polls=20000)
+    torch.cuda.synchronize()
+    assert api.decode_timed_out(dev) is True        # reported ...
+    assert api.decode_timed_out(dev) is False       # ... once
+    assert not np.array_equal(util.bf16_bits(out), _u16(c.bf16))   # the stalled decode did stop early
+    for _ in range(2):                               # and left the workspace and the GPU in working order
+        np.testing.assert_array_equal(_fp8_decode(c.fp8_u8.numpy(), art, n, m, dev), _u16(c.bf16))
+    assert api.decode_timed_out(dev) is False
+
+
 def test_fp8_repeated_calls_reuse_workspace(dev):
     n, m = 256, 1024
     c = wl.quantize_fp8(wl.random_weight(n, m, 3, "normal"), "channel")

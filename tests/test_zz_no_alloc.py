@@ -54,6 +54,10 @@ def test_noalloc_matches_regular_entry_twice(shape, mode):
         _lib.check(lib.mps_decode_fp8_noalloc(*_args(ctx, d, n, m, out), stream))
         torch.cuda.synchronize()
         np.testing.assert_array_equal(util.bf16_bits(out), want, err_msg=f"call {call}")
+    # a caller of this entry has no workspace to ask about; the status call takes NULL for the library's own
+    from mpserve_b200 import api
+
+    assert api.noalloc_decode_timed_out(dev) is False
 
 
 def test_noalloc_rejects_oversized_input():
