@@ -363,21 +363,44 @@ __global__ void bucket_table_kernel(const uint32_t* __restrict__ ctx_key, int G,
     }
 }
 
-// first-appearance list of a bucket's tables and context -> position in it (build_huffman.cu:748-783)
-__global__ void bucket_unique_kernel(const int32_t* __restrict__ bt, long long B, int32_t* __restrict__ U,
-                                     int32_t* __restrict__ uniq, int16_t* __restrict__ uidx) {
-    for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < B; b += (long long)gridDim.x * blockDim.x) {
+// first-appearance list of a bucket's tables and context -> position in it (build_huffman.cu:748-783).
+// One warp per bucket walks the 256 contexts 32 at a time: every lane first looks its table id up in
+// the list built so far (kept in shared memory), the lanes that bring a new id are grouped by value
+// with a warp match, and the lowest lane of each group appends the id at the position its rank
+// among those leaders gives, which is the order a sequential scan would have appended them in.
+constexpr int kUniqueWarps = 4;
+__global__ void __launch_bounds__(kUniqueWarps * 32)
+bucket_unique_kernel(const int32_t* __restrict__ bt, long long B, int32_t* __restrict__ U, int32_t* __restrict__ uniq,
+                     int16_t* __restrict__ uidx) {
+    __shared__ int32_t s_list[kUniqueWarps][256];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int32_t* list = s_list[w];
+    for (long long b = (long long)blockIdx.x * kUniqueWarps + w; b < B; b += (long long)gridDim.x * kUniqueWarps) {
         int32_t u = 0;
-        for (int i = 0; i < 256; ++i) { uniq[b * 256 + i] = -1; uidx[b * 256 + i] = -1; }
-        for (int i = 0; i < 256; ++i) {
-            const int32_t gid = bt[b * 256 + i];
-            if (gid < 0) continue;
-            int32_t found = -1;
-            for (int32_t j = 0; j < u; ++j) if (uniq[b * 256 + j] == gid) { found = j; break; }
-            if (found < 0) { uniq[b * 256 + u] = gid; found = u++; }
-            uidx[b * 256 + i] = (int16_t)found;
+        for (int c0 = 0; c0 < 256; c0 += 32) {
+            const int32_t gid = bt[b * 256 + c0 + lane];
+            const bool valid = gid >= 0;
+            int32_t pos = -1;
+            if (valid)
+                for (int32_t j = 0; j < u; ++j)
+                    if (list[j] == gid) { pos = j; break; }
+            const bool fresh = valid && pos < 0;
+            // lanes without a new id get a key no other lane has (-1 - lane is below every table id)
+            const uint32_t same = __match_any_sync(0xFFFFFFFFu, fresh ? gid : -1 - lane);
+            const int first = __ffs(same) - 1;
+            const bool leader = fresh && first == lane;
+            const uint32_t leaders = __ballot_sync(0xFFFFFFFFu, leader);
+            int32_t mine = u + __popc(leaders & ((1u << lane) - 1u));
+            if (leader) list[mine] = gid;
+            mine = __shfl_sync(0xFFFFFFFFu, mine, first);
+            if (fresh) pos = mine;
+            uidx[b * 256 + c0 + lane] = (int16_t)pos;
+            u += __popc(leaders);
+            __syncwarp();
         }
-        U[b] = u;
+        for (int j = lane; j < 256; j += 32) uniq[b * 256 + j] = (j < u) ? list[j] : -1;
+        if (lane == 0) U[b] = u;
+        __syncwarp();
     }
 }
 
@@ -887,7 +910,8 @@ int mps_build_bucket_unique(const int32_t* bucket_table_i32, int64_t num_buckets
         return MPS_ERR_INVALID;
     }
     if (num_buckets == 0) return MPS_OK;
-    bucket_unique_kernel<<<grid_for(num_buckets, 64), 64, 0, static_cast<cudaStream_t>(stream)>>>(
+    bucket_unique_kernel<<<grid_for((num_buckets + kUniqueWarps - 1) / kUniqueWarps, 1), kUniqueWarps * 32, 0,
+                           static_cast<cudaStream_t>(stream)>>>(
         bucket_table_i32, num_buckets, bucket_U_i32, bucket_unique_gid_i32, bucket_fp8_uidx_i16);
     MPS_CUDA_TRY(cudaGetLastError());
     return MPS_OK;

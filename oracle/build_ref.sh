@@ -2,10 +2,11 @@
 # Compiles the reference's CPU encoder (kernel/build_huffman.cu, host-only C++ despite its suffix)
 # from the reference tree where it lies, plus the small binding in ref_recipe/, into
 # oracle/_ref/mpserve_ref_build.so.  Outputs go only to oracle/_ref/ (git-ignored).
-# usage: oracle/build_ref.sh [/path/to/reference]
+# usage: oracle/build_ref.sh [/path/to/reference]   (default: $MPSERVE_REFERENCE_ROOT, else ../reference
+#        beside this repository)
 set -euo pipefail
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-REF="${1:-/root/reference}"
+REF="${1:-${MPSERVE_REFERENCE_ROOT:-$HERE/../../reference}}"
 OUT="$HERE/_ref"
 [ -f "$REF/kernel/build_huffman.cu" ] || { echo "reference sources not found under $REF" >&2; exit 3; }
 mkdir -p "$OUT"

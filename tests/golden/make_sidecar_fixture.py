@@ -90,7 +90,8 @@ def make_checkpoints(bf16_dir: Path, fp8_dir: Path) -> dict[str, torch.Tensor]:
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MPSERVE_REFERENCE_ROOT", "/root/reference"))
+    beside = Path(__file__).resolve().parents[3] / "reference"
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MPSERVE_REFERENCE_ROOT") or beside)
     script = ref_root / "scripts" / "compress_llm_fp8_huffman.py"
     if not script.exists():
         raise SystemExit(f"reference compressor not found: {script}")

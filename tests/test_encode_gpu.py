@@ -196,3 +196,48 @@ def test_full_size_build_decode_checksum_on_device(n, m, k):
     assert torch.equal(out.view(torch.uint16), c.bf16.view(torch.uint16))
     acc = api.checksum_u16(out)
     assert int(acc.cpu()[0]) % (1 << 64) == int(c.bf16.view(torch.uint16).to(torch.int64).sum()) % (1 << 64)
+
+
+def test_bucket_unique_lists_with_repeats_and_holes():
+    """The first-appearance list of a bucket's tables, on a table with repeated ids (inside one group of
+    32 contexts and across groups), absent contexts and the extremes of zero and 256 distinct ids; the
+    expected result is the sequential scan of build_huffman.cu:748-783 written as a Python loop."""
+    import ctypes as C
+
+    from mpserve_b200 import _lib
+
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(5)
+    B = 37
+    bt = rng.integers(-1, 40, size=(B, 256), dtype=np.int32)           # many repeats, some holes
+    bt[0] = -1                                                          # no table at all
+    bt[1] = np.arange(256, dtype=np.int32)[::-1] + 1000                 # all distinct
+    bt[2] = 7                                                           # a single id
+    bt[3] = np.repeat(np.arange(8, dtype=np.int32), 32)                 # one id per group of 32
+    bt[4] = np.tile(np.arange(32, dtype=np.int32), 8)                   # every group repeats the first
+    bt[5:9] = rng.integers(-1, 100000, size=(4, 256), dtype=np.int32)   # mostly distinct
+    want_u = np.zeros(B, np.int32)
+    want_list = np.full((B, 256), -1, np.int32)
+    want_idx = np.full((B, 256), -1, np.int16)
+    for b in range(B):
+        seen: dict[int, int] = {}
+        for i in range(256):
+            g = int(bt[b, i])
+            if g < 0:
+                continue
+            if g not in seen:
+                seen[g] = len(seen)
+                want_list[b, seen[g]] = g
+            want_idx[b, i] = seen[g]
+        want_u[b] = len(seen)
+    bt_d = torch.from_numpy(bt).to(dev)
+    U = torch.full((B,), -7, dtype=torch.int32, device=dev)
+    uniq = torch.full((B, 256), -7, dtype=torch.int32, device=dev)
+    uidx = torch.full((B, 256), -7, dtype=torch.int16, device=dev)
+    _lib.check(lib.mps_build_bucket_unique(bt_d.data_ptr(), B, U.data_ptr(), uniq.data_ptr(), uidx.data_ptr(),
+                                           C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(U.cpu().numpy(), want_u)
+    np.testing.assert_array_equal(uniq.cpu().numpy(), want_list)
+    np.testing.assert_array_equal(uidx.cpu().numpy(), want_idx)

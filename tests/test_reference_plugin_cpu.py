@@ -1,6 +1,6 @@
 """The reference's UNMODIFIED vLLM plugin, driven end to end on the host.
 
-Runs only where the reference tree is mounted (``MPSERVE_REFERENCE_ROOT``, default ``/root/reference``);
+Runs only where the reference tree is mounted (``MPSERVE_REFERENCE_ROOT``, else a ``reference`` directory beside this repository);
 elsewhere it skips.  ``scripts/mpserve_vllm_fp8_huffman.py`` is imported as it is; its
 ``create_weights`` registers the parameters, its weight loaders take the tensors of the sidecar
 fixture (written by the reference's own compressor, see tests/golden/make_sidecar_fixture.py), and its
@@ -26,7 +26,7 @@ import torch
 
 from tests._util import GOLDEN_DIR
 
-REF_ROOT = Path(os.environ.get("MPSERVE_REFERENCE_ROOT", "/root/reference"))
+REF_ROOT = Path(os.environ.get("MPSERVE_REFERENCE_ROOT") or Path(__file__).resolve().parents[2] / "reference")
 PLUGIN = REF_ROOT / "scripts" / "mpserve_vllm_fp8_huffman.py"
 FIXTURE = GOLDEN_DIR / "tiny_llama_sidecar"
 PREFIX = "model.layers.0"
