@@ -28,9 +28,10 @@ __all__ = [
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
 
-def _workspace(device: torch.device) -> torch.Tensor:
+def _workspace(device: torch.device, stream=None) -> torch.Tensor:
     """Zeroed queue counters, one per (device, stream); kernels hand them back zeroed."""
-    stream = torch.cuda.current_stream(device)
+    if stream is None:
+        stream = torch.cuda.current_stream(device)
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream.cuda_stream)
     ws = _workspaces.get(key)
     if ws is None:
@@ -220,28 +221,85 @@ def huffman_decode_fp8(fp8_params_u8, bitstream_u64, decode_syms_u16, decode_len
     signature) names a contiguous BF16 ``[n, m]`` tensor to decode into instead: a row range of a fused
     ``qkv`` / ``gate_up`` weight, or a buffer kept across forwards.
     """
-    n, m, max_len, B, k, tensors = validate_decode_fp8(
-        fp8_params_u8, bitstream_u64, decode_syms_u16, decode_lens_u8, bucket_table_i32, bucket_col_start_i32,
-        bucket_col_len_i32, bucket_row_offsets_i32, row_indices_i32, bucket_thread_startbit_u32,
-        bucket_bit_base_i64, n, m, max_len)
-    dev = _same_device(tensors)
+    tensors = (fp8_params_u8, bitstream_u64, decode_syms_u16, decode_lens_u8, bucket_table_i32, bucket_col_start_i32,
+               bucket_col_len_i32, bucket_row_offsets_i32, row_indices_i32, bucket_thread_startbit_u32,
+               bucket_bit_base_i64)
+    try:
+        key = (*map(id, tensors), n, m, max_len)
+        memo = _fp8_checked.get(key)
+    except TypeError:   # an argument that cannot be hashed takes the full checks, which name it
+        key = memo = None
+    if memo is None or not memo.still_holds(tensors):
+        memo = _CheckedFp8(*validate_decode_fp8(*tensors, n, m, max_len))
+        if key is not None:
+            if len(_fp8_checked) >= _CHECKED_CAP:
+                _fp8_checked.clear()
+            _fp8_checked[key] = memo
+    dev = memo.device
     if out is None:
-        out = torch.empty((n, m), dtype=torch.bfloat16, device=dev)
+        out = torch.empty((memo.n, memo.m), dtype=torch.bfloat16, device=dev)
     else:
         _check_cuda_contig(out, "out")
-        if out.dtype != torch.bfloat16 or out.numel() != n * m or out.device != dev:
+        if out.dtype != torch.bfloat16 or out.numel() != memo.n * memo.m or out.device != dev:
             raise ValueError("out must be a contiguous bfloat16 CUDA tensor of n*m elements on the inputs' device")
-    with torch.cuda.device(dev):
-        ws = _workspace(dev)
-        rc = _lib.load().mps_decode_fp8(
-            fp8_params_u8.data_ptr(), bitstream_u64.data_ptr(), bitstream_u64.numel(), decode_syms_u16.data_ptr(),
-            decode_lens_u8.data_ptr(), decode_syms_u16.size(0), bucket_table_i32.data_ptr(),
-            bucket_col_start_i32.data_ptr(), bucket_col_len_i32.data_ptr(), bucket_row_offsets_i32.data_ptr(),
-            row_indices_i32.data_ptr(), row_indices_i32.numel(), bucket_thread_startbit_u32.data_ptr(),
-            bucket_bit_base_i64.data_ptr(), B, k, n, m, max_len, out.data_ptr(), ws.data_ptr(),
-            ws.numel() * 4, _stream_ptr(dev))
+    desc = _lib.BucketTensor.from_buffer_copy(memo.desc)   # a private copy: concurrent callers share the memo
+    desc.out = out.data_ptr()
+    if torch.cuda.current_device() == memo.device_index:
+        stream = torch.cuda.current_stream(dev)
+        ws = _workspace(dev, stream)
+        rc = _lib.load().mps_decode_bucket_tensor(C.byref(desc), ws.data_ptr(), ws.numel() * 4, stream.cuda_stream)
+    else:
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream(dev)
+            ws = _workspace(dev, stream)
+            rc = _lib.load().mps_decode_bucket_tensor(C.byref(desc), ws.data_ptr(), ws.numel() * 4, stream.cuda_stream)
     _lib.check(rc)
     return out
+
+
+class _CheckedFp8:
+    """What one full argument check of ``huffman_decode_fp8`` established, kept so that the next call with
+    the same tensor objects only has to confirm that nothing about them changed: a serving loop decodes
+    the same weights on every forward, and the checks cost more host time than the launch.  Holds weak
+    references only, so it keeps no device memory alive."""
+
+    __slots__ = ("refs", "facts", "desc", "n", "m", "device", "device_index")
+
+    def __init__(self, n, m, max_len, B, k, tensors):
+        import weakref
+
+        (fp8_params_u8, bitstream_u64, decode_syms_u16, decode_lens_u8, bucket_table_i32, bucket_col_start_i32,
+         bucket_col_len_i32, bucket_row_offsets_i32, row_indices_i32, bucket_thread_startbit_u32,
+         bucket_bit_base_i64) = tensors
+        self.device = _same_device(tensors)
+        self.device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.refs = tuple(weakref.ref(t) for t in tensors)
+        self.facts = tuple((t.data_ptr(), t.shape, t.dtype) for t in tensors)
+        self.n, self.m = n, m
+        d = _lib.BucketTensor()
+        d.ctx_bytes = fp8_params_u8.data_ptr()
+        d.bitstream = bitstream_u64.data_ptr(); d.bitstream_words = bitstream_u64.numel()
+        d.decode_syms = decode_syms_u16.data_ptr(); d.decode_lens = decode_lens_u8.data_ptr()
+        d.num_tables = decode_syms_u16.size(0)
+        d.bucket_table = bucket_table_i32.data_ptr()
+        d.bucket_col_start = bucket_col_start_i32.data_ptr(); d.bucket_col_len = bucket_col_len_i32.data_ptr()
+        d.bucket_row_offsets = bucket_row_offsets_i32.data_ptr(); d.row_indices = row_indices_i32.data_ptr()
+        d.num_rows = row_indices_i32.numel()
+        d.thread_startbit = bucket_thread_startbit_u32.data_ptr(); d.bucket_bit_base = bucket_bit_base_i64.data_ptr()
+        d.num_buckets = B
+        d.k = k
+        d.mode, d.n, d.m = 0, n, m
+        self.desc = d
+
+    def still_holds(self, tensors) -> bool:
+        for t, ref, (ptr, shape, dtype) in zip(tensors, self.refs, self.facts):
+            if ref() is not t or t.data_ptr() != ptr or t.shape != shape or t.dtype is not dtype or not t.is_contiguous():
+                return False
+        return True
+
+
+_fp8_checked: dict[tuple, _CheckedFp8] = {}
+_CHECKED_CAP = 4096
 
 
 def huffman_decode_awq_int4_bucket(int4_values_u8, bitstream_u64, decode_syms_u16, decode_lens_u8, bucket_table_i32,

@@ -246,6 +246,44 @@ def test_fp8_argument_validation(dev):
         MPServe_cuda.huffman_decode_fp8(*bad)
 
 
+def test_fp8_checked_arguments_are_remembered_but_rechecked_when_they_change(dev):
+    """A second call with the same tensor objects skips the argument checks; a tensor changed in place
+    between two calls (another dtype, another shape, other storage) is checked again in full."""
+    import MPServe_cuda
+    from mpserve_b200 import api
+
+    n, m = 256, 1024
+    c = wl.quantize_fp8(wl.random_weight(n, m, 8, "normal"), "tensor")
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
+    d = util.artifacts_to_device(art, dev)
+    args = list(util.decode_fp8_args(c.fp8_u8.to(dev), d, n, m, 7))
+    want = _u16(c.bf16)
+    api._fp8_checked.clear()
+    np.testing.assert_array_equal(util.bf16_bits(MPServe_cuda.huffman_decode_fp8(*args)), want)
+    assert len(api._fp8_checked) == 1
+    memo = next(iter(api._fp8_checked.values()))
+    assert memo.still_holds(args[:11])
+    np.testing.assert_array_equal(util.bf16_bits(MPServe_cuda.huffman_decode_fp8(*args)), want)
+    assert len(api._fp8_checked) == 1 and next(iter(api._fp8_checked.values())) is memo
+
+    table = args[4]
+    kept = table.data
+    table.data = kept.to(torch.int64)                       # same object, another dtype
+    assert not memo.still_holds(args[:11])
+    with pytest.raises(ValueError, match="int32"):
+        MPServe_cuda.huffman_decode_fp8(*args)
+    table.data = kept[:, :128].contiguous()                 # same object, another shape
+    with pytest.raises(ValueError, match=r"\[B,256\]"):
+        MPServe_cuda.huffman_decode_fp8(*args)
+    table.data = kept.clone()                               # same object, same facts, other storage
+    assert not memo.still_holds(args[:11])
+    np.testing.assert_array_equal(util.bf16_bits(MPServe_cuda.huffman_decode_fp8(*args)), want)
+    # a new tensor object is a new entry, never a stale hit
+    fresh = list(args)
+    fresh[4] = kept.clone()
+    np.testing.assert_array_equal(util.bf16_bits(MPServe_cuda.huffman_decode_fp8(*fresh)), want)
+
+
 def test_fp8_batch_plan_matches_single(dev):
     # per-channel tensors of this size have tiny buckets (decoded one by one, in place); the per-tensor
     # ones have full 128-row buckets and share the persistent launch
