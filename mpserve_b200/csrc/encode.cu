@@ -1,8 +1,9 @@
 // GPU builder of the Huffman sidecar: replaces the single-threaded CPU encoder of the reference
 // (kernel/build_huffman.cu) with device passes that produce byte-identical artifacts.
 //
-//   analyze    composite keys (scale, context, symbol) -> radix sort -> run lengths: the histogram
-//              of every context (build_huffman.cu:392-412), contexts in ascending key order
+//   analyze    the histogram of every context (build_huffman.cu:392-412), contexts in ascending key
+//              order: a two-level count, by scale and then by context, with no sort over the elements
+//              (histogram.cuh); then each context's items ordered by (count, symbol)
 //   codebooks  per context: order by (count, symbol), ESC reduction when there are more symbols than
 //              table slots (:479-535), length-limited code lengths (package-merge, :46-118), canonical
 //              codes in item order (:171-203), lookup-table fill and 4-bit length packing (:205-239)
@@ -10,15 +11,16 @@
 //              sums per bucket, 64-bit aligned bucket bases (:811-879)
 //   emit       the same walk again, writing codes MSB-first with one 64-bit atomic OR per word (:881-911)
 //
-// The global sorts and scans use CUB (device-wide radix sort / run-length encode / scan from the
-// CUDA toolkit); everything codec-specific is written here.  Bucket row lists are small host-side
+// Scans, and the sorts of the distinct (context, symbol) items -- a hundredth of the elements for a
+// quantised weight -- use CUB (device-wide scan / radix sort from the CUDA toolkit); everything that
+// touches every element is written here.  Bucket row lists are small host-side
 // metadata and are built by the caller from the scale tensor (mpserve_b200/encoder.py).
 #include <cub/device/device_radix_sort.cuh>
-#include <cub/device/device_run_length_encode.cuh>
 #include <cub/device/device_scan.cuh>
 
 #include <string.h>
 
+#include "histogram.cuh"
 #include "mps_common.cuh"
 
 namespace mps {
@@ -60,47 +62,19 @@ enum { V_FP8 = 0, V_AWQ_BUCKET = 1, V_AWQ_BYSCALE = 2, V_AWQ_SHARED = 3 };
 // ------------------------------------------------------------------------------------------------
 // analyze
 // ------------------------------------------------------------------------------------------------
-// scale_mode: 0 scalar, 1 per row, 2 two-dimensional blocks [nb0, nb1] of sb0 x sb1 elements
-__global__ void make_composites_kernel(const uint16_t* __restrict__ sym, const uint8_t* __restrict__ ctx,
-                                       const uint16_t* __restrict__ scales, int scale_mode, long long m, long long nb1,
-                                       long long sb0, long long sb1, uint32_t ctx_mask, long long numel,
-                                       unsigned long long* __restrict__ comp) {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += (long long)gridDim.x * blockDim.x) {
-        long long sidx = 0;
-        if (scale_mode != 0) {
-            const long long r = i / m;
-            sidx = (scale_mode == 1) ? r : (r / sb0) * nb1 + (i - r * m) / sb1;
-        }
-        comp[i] = ((unsigned long long)scales[sidx] << 32) | ((unsigned long long)(ctx[i] & ctx_mask) << 16) | sym[i];
-    }
-}
-
-__global__ void context_heads_kernel(const unsigned long long* __restrict__ items, long long N, int* __restrict__ head) {
-    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < N; j += (long long)gridDim.x * blockDim.x)
-        head[j] = (j == 0 || (items[j] >> 16) != (items[j - 1] >> 16)) ? 1 : 0;
-}
-
-// cid = inclusive scan of head; context g starts where head is set
-__global__ void context_offsets_kernel(const unsigned long long* __restrict__ items, const int* __restrict__ head,
-                                       const int* __restrict__ cid, long long N, int* __restrict__ ctx_ofs,
-                                       uint32_t* __restrict__ ctx_key) {
-    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < N; j += (long long)gridDim.x * blockDim.x) {
-        if (head[j]) {
-            const int g = cid[j] - 1;
-            ctx_ofs[g] = (int)j;
-            ctx_key[g] = (uint32_t)(items[j] >> 16);
-        }
-        if (j == N - 1) ctx_ofs[cid[j]] = (int)N;
-    }
-}
-
+// keys that order the items of every context by (count, symbol), and the context of every item
 __global__ void item_sort_keys_kernel(const unsigned long long* __restrict__ items, const int* __restrict__ counts,
-                                      const int* __restrict__ cid, long long N, unsigned long long* __restrict__ k1,
+                                      const int* __restrict__ ctx_ofs, int G, long long N, unsigned long long* __restrict__ k1,
                                       int* __restrict__ v, uint32_t* __restrict__ ctx_of_item) {
     for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < N; j += (long long)gridDim.x * blockDim.x) {
         k1[j] = ((unsigned long long)(uint32_t)counts[j] << 16) | (items[j] & 0xFFFFull);
         v[j] = (int)j;
-        ctx_of_item[j] = (uint32_t)(cid[j] - 1);
+        int lo = 0, hi = G;  // last context that starts at or before item j
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if ((long long)ctx_ofs[mid] <= j) lo = mid; else hi = mid;
+        }
+        ctx_of_item[j] = (uint32_t)lo;
     }
 }
 
@@ -740,8 +714,11 @@ extern "C" {
 size_t mps_build_workspace_bytes(int64_t numel, int64_t substreams) {
     if (numel < 0) numel = 0;
     if (substreams < numel) substreams = numel;
+    // (the last term: six 32-bit arrays over the (scale, context) segments, of which a tensor has at most
+    // 256 per distinct scale and no more distinct scales than elements or 16-bit values)
+    const size_t max_scales = (size_t)(numel < 65536 ? numel : 65536);
     return 256 + (size_t)numel * 34 + (size_t)numel * 40 + (size_t)substreams * 4 + cub_temp_bytes(numel) + kCodebookScratch +
-           (1ull << 20);
+           (4ull << 20) + (max_scales * 256 + 1) * 24;
 }
 
 int mps_build_analyze(mps_build_state* state, const uint16_t* bf16_bits, const uint8_t* ctx_bytes,
@@ -780,35 +757,108 @@ int mps_build_analyze(mps_build_state* state, const uint16_t* bf16_bits, const u
     auto* escsym = C.take<uint16_t>(numel);           S.o_escsym = (uint8_t*)escsym - S.ws;
     C.off = align_up(C.off);
     S.o_scratch = C.off; S.scratch_bytes = workspace_bytes - C.off;
-    // scratch of this call
-    auto* comp_a = C.take<unsigned long long>(numel);
-    auto* comp_b = C.take<unsigned long long>(numel);
-    auto* d_runs = C.take<long long>(4);
+    // ---- scratch of the histogram ------------------------------------------------------------------
+    MPS_CUDA_TRY(cudaMemsetAsync(S.d_flag, 0, 256, st));
+    hist::Geom g;
+    g.n = n; g.m = m; g.scale_mode = scale_mode;
+    g.ctx_mask = (variant == V_FP8) ? 0xFFu : 0x0Fu;
+    g.nctx = (variant == V_FP8) ? 256 : 16;
+    if (scale_mode == 2) {
+        if (nb1 * sb1 < m) { set_error("unsupported scales layout"); return MPS_ERR_INVALID; }
+        g.ub0 = sb0; g.ub1 = sb1; g.nbu1 = nb1; g.nbu0 = (n + sb0 - 1) / sb0;
+    } else {  // pieces of rows
+        g.ub0 = 1; g.ub1 = (m <= 8192) ? m : 4096; g.nbu1 = (m + g.ub1 - 1) / g.ub1; g.nbu0 = n;
+    }
+    const long long units = g.nbu0 * g.nbu1;
     const size_t kCubTempBytes = cub_temp_bytes(numel);
     void* cub_tmp = C.take<uint8_t>(kCubTempBytes);
+    auto* per_scale = C.take<uint32_t>(hist::kScaleValues + 1);   // units of every scale value
+    auto* unit_ofs = C.take<uint32_t>(hist::kScaleValues + 1);
+    auto* rank = C.take<uint32_t>(hist::kScaleValues + 1);        // flags, then ranks; [65536] = number of distinct scales
+    auto* unit_cur = C.take<uint32_t>(hist::kScaleValues);
+    auto* scale_of_rank = C.take<uint16_t>(hist::kScaleValues);
+    auto* unit_sorted = C.take<uint32_t>(units);
+    auto* seg_syms = C.take<uint16_t>(numel);
+    auto* st_sym = C.take<uint16_t>(numel);
+    auto* st_cnt = C.take<uint32_t>(numel);
     if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
-
-    MPS_CUDA_TRY(cudaMemsetAsync(S.d_flag, 0, 256, st));
-    const uint32_t ctx_mask = (variant == V_FP8) ? 0xFFu : 0x0Fu;
-    make_composites_kernel<<<grid_for(numel), 256, 0, st>>>(bf16_bits, ctx_bytes, scales_u16, scale_mode, m, nb1, sb0, sb1,
-                                                            ctx_mask, numel, comp_a);
-    MPS_CUDA_TRY(cudaGetLastError());
     size_t need = 0;
-    MPS_CUDA_TRY(cub::DeviceRadixSort::SortKeys(nullptr, need, comp_a, comp_b, (int)numel, 0, 48, st));
-    if (need > kCubTempBytes) { set_error("sort temporary storage exceeds the reserved %zu bytes", kCubTempBytes); return MPS_ERR_WORKSPACE; }
+
+    // scales: rank of every distinct value, units listed by scale
+    MPS_CUDA_TRY(cudaMemsetAsync(per_scale, 0, (hist::kScaleValues + 1) * sizeof(uint32_t), st));
+    hist::unit_scale_count_kernel<<<grid_for(units), 256, 0, st>>>(g, scales_u16, units, per_scale);
+    hist::scale_flags_kernel<<<hist::kScaleValues / 256, 256, 0, st>>>(per_scale, rank);
     need = kCubTempBytes;
-    MPS_CUDA_TRY(cub::DeviceRadixSort::SortKeys(cub_tmp, need, comp_a, comp_b, (int)numel, 0, 48, st));
+    MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(cub_tmp, need, per_scale, unit_ofs, hist::kScaleValues + 1, st));
     need = kCubTempBytes;
-    MPS_CUDA_TRY(cub::DeviceRunLengthEncode::Encode(cub_tmp, need, comp_b, items, counts, d_runs, (int)numel, st));
-    long long N = 0;
-    MPS_CUDA_TRY(cudaMemcpyAsync(&N, d_runs, sizeof(N), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(cub_tmp, need, rank, rank, hist::kScaleValues + 1, st));
+    hist::scale_ranks_kernel<<<hist::kScaleValues / 256, 256, 0, st>>>(per_scale, rank, unit_ofs, scale_of_rank, unit_cur);
+    hist::unit_scatter_kernel<<<grid_for(units), 256, 0, st>>>(g, scales_u16, units, unit_cur, unit_sorted);
+    uint32_t num_scales = 0;
+    MPS_CUDA_TRY(cudaMemcpyAsync(&num_scales, rank + hist::kScaleValues, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
     MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    const long long nseg = (long long)num_scales * g.nctx;
+
+    // segments (scale rank, context): sizes, offsets, symbols
+    auto* seg_cnt = C.take<uint32_t>(nseg + 1);
+    auto* seg_ofs = C.take<uint32_t>(nseg + 1);
+    auto* seg_cur = C.take<uint32_t>(nseg + 1);      // write cursors, later distinct symbols per segment, then item offsets
+    auto* chunk_ofs = C.take<uint32_t>(nseg + 1);    // chunks per segment, then their prefix
+    auto* split_id = C.take<uint32_t>(nseg + 1);     // split flags, then their prefix
+    auto* ctx_id = C.take<uint32_t>(nseg + 1);       // non-empty flags, then their prefix: the context index
+    if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
+    long long upw = hist::kWarpElems / (g.ub0 * g.ub1);
+    if (upw < 1) upw = 1;
+    const long long walk_warps = (units + upw - 1) / upw;
+    const unsigned walk_grid = (unsigned)((walk_warps + hist::kWalkWarps - 1) / hist::kWalkWarps);
+    MPS_CUDA_TRY(cudaMemsetAsync(seg_cnt, 0, (nseg + 1) * sizeof(uint32_t), st));
+    hist::segment_walk_kernel<false><<<walk_grid, hist::kWalkWarps * 32, 0, st>>>(g, bf16_bits, ctx_bytes, scales_u16, rank, unit_sorted,
+                                                                                  units, upw, seg_cnt, nullptr);
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(cub_tmp, need, seg_cnt, seg_ofs, (int)(nseg + 1), st));
+    MPS_CUDA_TRY(cudaMemcpyAsync(seg_cur, seg_ofs, (nseg + 1) * sizeof(uint32_t), cudaMemcpyDeviceToDevice, st));
+    hist::segment_walk_kernel<true><<<walk_grid, hist::kWalkWarps * 32, 0, st>>>(g, bf16_bits, ctx_bytes, scales_u16, rank, unit_sorted,
+                                                                                 units, upw, seg_cur, seg_syms);
+    hist::chunk_plan_kernel<<<grid_for(nseg + 1), 256, 0, st>>>(seg_cnt, nseg, chunk_ofs, split_id, ctx_id);
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(cub_tmp, need, chunk_ofs, chunk_ofs, (int)(nseg + 1), st));
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(cub_tmp, need, split_id, split_id, (int)(nseg + 1), st));
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(cub_tmp, need, ctx_id, ctx_id, (int)(nseg + 1), st));
+    uint32_t totals[3] = {0, 0, 0};  // chunks, split segments, contexts
+    MPS_CUDA_TRY(cudaMemcpyAsync(&totals[0], chunk_ofs + nseg, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaMemcpyAsync(&totals[1], split_id + nseg, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaMemcpyAsync(&totals[2], ctx_id + nseg, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    const long long num_chunks = totals[0], num_split = totals[1];
+    const int G = (int)totals[2];
+
+    // symbols of every segment counted by value
+    auto* chunk_seg = C.take<uint32_t>(num_chunks);
+    auto* split_seg = C.take<uint32_t>(num_split);
+    auto* dense = C.take<uint32_t>((size_t)num_split * 65536u);
+    if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
+    hist::chunk_fill_kernel<<<grid_for(nseg), 256, 0, st>>>(seg_cnt, nseg, chunk_ofs, split_id, chunk_seg, split_seg);
+    if (num_split) MPS_CUDA_TRY(cudaMemsetAsync(dense, 0, (size_t)num_split * 65536u * sizeof(uint32_t), st));
+    MPS_CUDA_TRY(cudaMemsetAsync(seg_cur, 0, (nseg + 1) * sizeof(uint32_t), st));
+    if (num_chunks)
+        hist::chunk_count_kernel<<<(unsigned)num_chunks, 256, 0, st>>>(seg_syms, seg_cnt, seg_ofs, chunk_seg, chunk_ofs, split_id, dense,
+                                                                       st_sym, st_cnt, seg_cur);
+    if (num_split) hist::split_finish_kernel<<<(unsigned)num_split, 256, 0, st>>>(split_seg, seg_ofs, dense, st_sym, st_cnt, seg_cur);
+    need = kCubTempBytes;
+    MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(cub_tmp, need, seg_cur, seg_cur, (int)(nseg + 1), st));
+    hist::gather_items_kernel<<<grid_for(nseg * 32), 256, 0, st>>>(seg_cnt, seg_ofs, seg_cur, ctx_id, nseg, g.nctx, scale_of_rank, st_sym,
+                                                                   st_cnt, items, counts, ctx_ofs, ctx_key);
+    uint32_t n_items = 0;
+    MPS_CUDA_TRY(cudaMemcpyAsync(&n_items, seg_cur + nseg, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    MPS_CUDA_TRY(cudaGetLastError());
+    MPS_CUDA_TRY(cudaStreamSynchronize(st));
+    const long long N = n_items;
     S.N = N;
 
-    // contexts: heads -> ids -> offsets and keys
-    C.off = S.o_scratch;  // the composites are no longer needed
-    auto* head = C.take<int>(N);
-    auto* cid = C.take<int>(N);
+    // ---- scratch of the per-context ordering (the histogram's is no longer needed) ---------------------
+    C.off = S.o_scratch;
     auto* k1 = C.take<unsigned long long>(N);
     auto* k1o = C.take<unsigned long long>(N);
     auto* v = C.take<int>(N);
@@ -817,14 +867,8 @@ int mps_build_analyze(mps_build_state* state, const uint16_t* bf16_bits, const u
     auto* cio = C.take<uint32_t>(N);
     cub_tmp = C.take<uint8_t>(kCubTempBytes);
     if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
-    context_heads_kernel<<<grid_for(N), 256, 0, st>>>(items, N, head);
-    need = kCubTempBytes;
-    MPS_CUDA_TRY(cub::DeviceScan::InclusiveSum(cub_tmp, need, head, cid, (int)N, st));
-    context_offsets_kernel<<<grid_for(N), 256, 0, st>>>(items, head, cid, N, ctx_ofs, ctx_key);
-    int G = 0;
-    MPS_CUDA_TRY(cudaMemcpyAsync(&G, cid + (N - 1), sizeof(int), cudaMemcpyDeviceToHost, st));
     // items of every context ordered by (count, symbol): sort by that key, then stably by context
-    item_sort_keys_kernel<<<grid_for(N), 256, 0, st>>>(items, counts, cid, N, k1, v, ci);
+    item_sort_keys_kernel<<<grid_for(N), 256, 0, st>>>(items, counts, ctx_ofs, G, N, k1, v, ci);
     need = kCubTempBytes;
     MPS_CUDA_TRY(cub::DeviceRadixSort::SortPairs(cub_tmp, need, k1, k1o, v, vo, (int)N, 0, 48, st));
     gather_u32_kernel<<<grid_for(N), 256, 0, st>>>(ci, vo, N, cio);
