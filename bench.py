@@ -49,7 +49,8 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch divided by its elements, from the ncu
 # capture summarised in profiles/ (traffic grows in proportion to the elements of a launch)
 NCU_TRAFFIC_BYTES_PER_ELEMENT = 3.757
-E2E_MAX_PINNED_BYTES = 24 << 30   # pinned host memory one rank may take for the end-to-end leg
+E2E_MAX_PINNED_BYTES = 24 << 30   # pinned host memory one rank may take for the end-to-end leg, at most
+E2E_PINNED_SHARE = 0.35           # ... and all ranks of the box together this share of the memory that is free
 
 DECODE_KEYS = ("bitstream_u64", "decode_syms_u16", "decode_lens_u8", "bucket_table_i32", "bucket_col_start_i32",
                "bucket_col_len_i32", "bucket_row_offsets_i32", "row_indices_i32", "bucket_thread_startbit_u32",
@@ -65,6 +66,44 @@ SIZES = [(128, 256), (256, 512), (512, 1024), (1024, 2048), (2048, 4096), (4096,
 
 def log(*a):
     print(*a, file=sys.stderr, flush=True)
+
+
+def pinned_allowance(local_world: int) -> int:
+    """Bytes of pinned host memory one rank may take: a share of what the box has free, split over its ranks."""
+    free = None
+    try:
+        for ln in open("/proc/meminfo"):
+            if ln.startswith("MemAvailable:"):
+                free = int(ln.split()[1]) * 1024
+                break
+    except OSError:
+        pass
+    if free is None:
+        return 4 << 30
+    return int(min(E2E_MAX_PINNED_BYTES, E2E_PINNED_SHARE * free / max(1, local_world)))
+
+
+def bind_near_gpu(local_rank: int):
+    """Keep this rank's threads on the CPUs of its GPU's NUMA node (pinned copies and launches then stay off the
+    inter-socket link).  Returns what was done, for the JSON line; does nothing on a single-node host."""
+    try:
+        props = torch.cuda.get_device_properties(local_rank)
+        base = Path(f"/sys/bus/pci/devices/{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0")
+        node = int((base / "numa_node").read_text())
+        nodes = [p for p in Path("/sys/devices/system/node").glob("node[0-9]*")]
+        if node < 0 or len(nodes) < 2:
+            return {"numa_node": node, "numa_nodes": len(nodes), "bound": False}
+        cpus = set()
+        for part in (base / "local_cpulist").read_text().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return {"numa_node": node, "numa_nodes": len(nodes), "bound": False}
+        os.sched_setaffinity(0, cpus)
+        return {"numa_node": node, "numa_nodes": len(nodes), "bound": True, "cpus": len(cpus)}
+    except Exception as e:  # noqa: BLE001 - best effort: a box without sysfs entries runs unbound
+        return {"bound": False, "why": type(e).__name__}
 
 
 def hbm_peak():
@@ -289,6 +328,9 @@ def run_ours(args, rank, world, local_rank):
     _lib.load()  # no fallback: a missing extension is an error
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    # (a lone rank stays unbound: its CPU baseline is meant to use every core of the box)
+    host_binding = bind_near_gpu(local_rank) if world > 1 else {"bound": False, "why": "single rank"}
+    pinned_cap = pinned_allowance(int(os.environ.get("LOCAL_WORLD_SIZE", world)))
     cfg, tp, wname, layers = workload_for(args.gpus, args.layers)
     # what a rank holds: compressed inputs (~1.75 B/element) and BF16 outputs; shorten the model rather than
     # run out of device memory, and say so in config.workload
@@ -329,10 +371,13 @@ def run_ours(args, rank, world, local_rank):
             views.append(v)
         it = iter(views)
         these = []
+        out_flat = torch.empty(sum(n * m for _, n, m, _, _ in layer), dtype=torch.bfloat16, device=dev)   # the layer's outputs
+        o0 = 0
         for name, n, m, c, art in layer:
             ctx = next(it)
             d = {k: next(it) for k in DECODE_KEYS}
-            these.append((ctx, d, torch.empty((n, m), dtype=torch.bfloat16, device=dev)))
+            these.append((ctx, d, out_flat[o0:o0 + n * m].view(n, m)))
+            o0 += n * m
             alg_bytes += n * m + sum(v.numel() * v.element_size() for v in d.values()) + 2 * n * m
             n_elem += n * m
             shapes.append((n, m))
@@ -342,13 +387,13 @@ def run_ours(args, rank, world, local_rank):
             assert torch.equal(out.view(torch.uint16), c.bf16.view(torch.uint16)), f"decode mismatch in layer {li} {name}"
             api.checksum_u16(c.bf16, want)
         host = None
-        if pinned + total <= E2E_MAX_PINNED_BYTES:
+        if pinned + total <= pinned_cap:
             host = torch.empty(total, dtype=torch.uint8, pin_memory=True)
             host.copy_(flat)
             pinned += total
             h2d_bytes += total
         entries.extend(these)
-        layer_entries.append((these, lp))
+        layer_entries.append((these, lp, out_flat))
         layer_bufs.append((flat, host))
         del layer, arrays, views
     torch.cuda.synchronize()
@@ -448,8 +493,13 @@ def run_ours(args, rank, world, local_rank):
     # ---- end to end: pinned host -> device copy of the compressed inputs, decode, checksum back ------
     # Layer i is decoded (and check-summed) on the compute stream while layer i+1 crosses PCIe on the copy
     # stream.  Layers whose inputs did not fit the pinned-memory allowance are left out of this leg.
-    e2e_layers = [(flat, host, lp, these) for (flat, host), (these, lp) in zip(layer_bufs, layer_entries) if host is not None]
-    e2e_out_bytes = sum(2 * o.numel() for _, _, _, these in e2e_layers for _, _, o in these)
+    e2e_layers = [(flat, host, lp, out_flat) for (flat, host), (these, lp, out_flat) in zip(layer_bufs, layer_entries)
+                  if host is not None]
+    e2e_out_bytes = sum(2 * out_flat.numel() for _, _, _, out_flat in e2e_layers)
+    e2e_want = torch.zeros(2, dtype=torch.int64, device=dev)   # what a step must read back: from the verified outputs
+    for _, _, _, out_flat in e2e_layers:
+        api.checksum_u16(out_flat, e2e_want)
+    e2e_want = e2e_want.cpu()
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream(dev)
     acc = torch.zeros(2, dtype=torch.int64, device=dev)
@@ -458,32 +508,33 @@ def run_ours(args, rank, world, local_rank):
     def e2e_step():
         acc.zero_()
         copy_stream.wait_stream(main_stream)   # the previous step's decodes have read the buffers
-        for flat_dev, flat_host, lp, these in e2e_layers:
+        for flat_dev, flat_host, lp, out_flat in e2e_layers:
             with torch.cuda.stream(copy_stream):
                 flat_dev.copy_(flat_host, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(copy_stream)
             main_stream.wait_event(ev)
-            for o in lp.decode():
-                api.checksum_u16(o, acc)
+            lp.decode()
+            api.checksum_u16(out_flat, acc)     # the layer's outputs are one buffer: one launch
         return acc.cpu()
 
-    e2e_step()
+    assert torch.equal(e2e_step(), e2e_want), "the end-to-end step read back another checksum than the verified outputs give"
     torch.cuda.synchronize()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
-        e2e_step()
+        e2e_got = e2e_step()
     e1.record()
     barrier()
     assert not api.decode_timed_out(dev), "a bounded wait ran out in the end-to-end leg"
+    assert torch.equal(e2e_got, e2e_want), "the end-to-end step read back another checksum than the verified outputs give"
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
     if use_dist:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t[0])
-    e2e_launches = e2e_steps * sum(1 + len(these) for _, _, _, these in e2e_layers)
+    e2e_launches = e2e_steps * 2 * len(e2e_layers)
 
     # ---- checksum of all ranks' outputs (outside every timed region; NCCL when there are several ranks) ----
     got = torch.zeros(2, dtype=torch.int64, device=dev)
@@ -541,12 +592,14 @@ def run_ours(args, rank, world, local_rank):
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 16,
                 "ms_per_step": e2e_ms, "steps": e2e_steps, "gpu_launches": e2e_launches, "layers": len(e2e_layers),
                 "how": "per layer: one pinned-host -> device copy of its packed compressed inputs on a copy stream, "
-                       "then one decode launch and the checksums on the compute stream; 16 bytes read back per step"
+                       "then one decode launch and one checksum launch on the compute stream; 16 bytes read back per step "
+                       "and compared with the checksum of the verified outputs"
                        + ("" if len(e2e_layers) == layers else
                           f"; {len(e2e_layers)} of {layers} layers (pinned-memory allowance), a rate over those")},
         "dropin": dropin,
         "gpu_launches": args.steps,
         "clocks": clocks,
+        "host": {"cpus": os.cpu_count(), "binding": host_binding, "pinned_allowance_bytes": pinned_cap},
     }
     print(json.dumps(line), flush=True)
 

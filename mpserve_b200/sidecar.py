@@ -97,6 +97,51 @@ def write_sidecar(path, modules: Mapping[str, tuple[torch.Tensor, Mapping[str, t
     save_file(tensors, str(path))
 
 
+# ---- tensor parallelism -----------------------------------------------------------------------------
+# A bitstream cannot be narrowed the way a weight loader narrows a checkpoint tensor to its rank's rows
+# or columns, which is why the reference's plugin refuses tp_size > 1 (scripts/
+# mpserve_vllm_fp8_huffman.py:165-168).  Here every rank gets a sidecar of its own, built from its
+# shards (mpserve_b200/shard.py: column-parallel layers split rows, row-parallel layers split columns),
+# and the file says which rank of which degree it is for, so that a loader running under another layout
+# fails at load time instead of decoding the wrong rows.
+
+def rank_sidecar_name(tp_rank: int, tp_size: int) -> str:
+    return "model.huffman.safetensors" if tp_size == 1 else f"model.huffman.tp{tp_size}-rank{tp_rank:02d}.safetensors"
+
+
+def write_rank_sidecar(directory, tp_rank: int, tp_size: int,
+                       modules: Mapping[str, tuple[torch.Tensor, Mapping[str, torch.Tensor]]]) -> Path:
+    """Write rank ``tp_rank``'s sidecar: ``modules`` as for ``write_sidecar``, built from this rank's shards."""
+    from safetensors.torch import save_file
+
+    if not 0 <= tp_rank < tp_size:
+        raise ValueError(f"tp_rank {tp_rank} outside tensor-parallel degree {tp_size}")
+    tensors: dict[str, torch.Tensor] = {}
+    for prefix, (fp8_u8, art) in modules.items():
+        tensors.update(sidecar_tensors(prefix, fp8_u8, art))
+    path = Path(directory) / rank_sidecar_name(tp_rank, tp_size)
+    save_file(tensors, str(path), metadata={"mpserve_tp_size": str(tp_size), "mpserve_tp_rank": str(tp_rank)})
+    return path
+
+
+def read_rank_sidecar(directory, tp_rank: int, tp_size: int, device=None) -> dict[str, dict[str, torch.Tensor]]:
+    """This rank's modules (as ``read_sidecar`` returns them).  Raises when the directory has no sidecar
+    for this layout or the file was written for another one."""
+    from safetensors import safe_open
+
+    path = Path(directory) / rank_sidecar_name(tp_rank, tp_size)
+    if not path.exists():
+        have = sorted(p.name for p in Path(directory).glob("model.huffman*.safetensors"))
+        raise FileNotFoundError(f"no Huffman sidecar for rank {tp_rank} of {tp_size} in {directory} (found: {have}); "
+                                "sidecars are built per tensor-parallel shard and cannot be re-split")
+    with safe_open(str(path), framework="pt", device="cpu") as f:
+        meta = f.metadata() or {}
+    said = (int(meta.get("mpserve_tp_size", "1")), int(meta.get("mpserve_tp_rank", "0")))
+    if said != (tp_size, tp_rank):
+        raise ValueError(f"{path.name} was written for rank {said[1]} of {said[0]}, not rank {tp_rank} of {tp_size}")
+    return read_sidecar(path, device=device)
+
+
 def as_decode_inputs(stored: Mapping[str, torch.Tensor]) -> dict[str, torch.Tensor]:
     """Re-view one module's stored tensors (keys without the ``huff_`` prefix) for the decode entry."""
     out = {}

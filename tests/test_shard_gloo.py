@@ -90,3 +90,76 @@ def test_checksum_all_reduce_two_ranks_gloo():
             bits = _full_weight(name, n, m, li).view(torch.uint16).numpy()
             whole = shard.combine(whole, shard.checksum_host(bits))
     assert whole[0] == want[0]
+
+
+# ---- per-rank sidecars: written and read back by two ranks, the shards re-assembled by the parent ------
+
+def _sidecar_worker(rank, world, port, directory, q):
+    import torch.distributed as dist
+
+    from mpserve_b200 import sidecar
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        modules, sources = {}, {}
+        for name, n, m in wl.layer_linears(TINY):
+            w = shard.shard_of(name, _full_weight(name, n, m, 0), world, rank)
+            c = wl.quantize_fp8(w, "channel")
+            bits = c.bf16.view(torch.uint16).numpy()
+            art = orc.build_fp8(bits, c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 64)
+            prefix = f"model.layers.0.{name}"
+            modules[prefix] = (c.fp8_u8, {k: torch.from_numpy(v) for k, v in art.items() if isinstance(v, np.ndarray)})
+            sources[prefix] = bits
+        sidecar.write_rank_sidecar(directory, rank, world, modules)
+        dist.barrier()
+        back = sidecar.read_rank_sidecar(directory, rank, world)
+        assert set(back) == set(modules)
+        decoded = {}
+        for prefix, entry in back.items():
+            n, m = entry["fp8_u8"].shape
+            art = {k: v.numpy() for k, v in entry.items() if k != "fp8_u8"}
+            decoded[prefix] = orc.decode_fp8(entry["fp8_u8"].numpy(), art, n, m)
+            assert np.array_equal(decoded[prefix], sources[prefix])
+        refusals = []
+        for wrong_rank, wrong_size in ((1 - rank, world), (rank, world + 2)):
+            try:
+                if (wrong_rank, wrong_size) == (1 - rank, world):   # the other rank's file under this rank's name
+                    other = sidecar.read_sidecar(os.path.join(directory, sidecar.rank_sidecar_name(1 - rank, world)))
+                    assert set(other) == set(modules)
+                    os.makedirs(os.path.join(directory, f"swap{rank}"), exist_ok=True)
+                    src = os.path.join(directory, sidecar.rank_sidecar_name(1 - rank, world))
+                    dst = os.path.join(directory, f"swap{rank}", sidecar.rank_sidecar_name(rank, world))
+                    with open(src, "rb") as a, open(dst, "wb") as b:
+                        b.write(a.read())
+                    sidecar.read_rank_sidecar(os.path.join(directory, f"swap{rank}"), rank, world)
+                else:
+                    sidecar.read_rank_sidecar(directory, wrong_rank, wrong_size)
+                refusals.append(None)
+            except (ValueError, FileNotFoundError) as e:
+                refusals.append(type(e).__name__)
+        q.put((rank, decoded, refusals))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rank_sidecars_two_ranks_gloo(tmp_path):
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_sidecar_worker, args=(r, world, port, str(tmp_path), q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict((r, (d, ref)) for r, d, ref in (q.get(timeout=180) for _ in range(world)))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for r in range(world):
+        # a file written for the other rank, and a layout nobody wrote, are both refused at load time
+        assert results[r][1] == ["ValueError", "FileNotFoundError"]
+    for name, n, m in wl.layer_linears(TINY):
+        prefix = f"model.layers.0.{name}"
+        dim = 1 if name.endswith(("o_proj", "down_proj")) else 0
+        whole = np.concatenate([results[r][0][prefix] for r in range(world)], axis=dim)
+        assert np.array_equal(whole, _full_weight(name, n, m, 0).view(torch.uint16).numpy())
