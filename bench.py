@@ -272,6 +272,20 @@ def run_reference(args, rank, world):
     cores = os.cpu_count() or 1
     orc.set_num_threads(cores)   # not what a launcher exported: torchrun sets OMP_NUM_THREADS=1
     cores = orc.num_threads()
+    if args.workload == "build":
+        enc = cpu_encode_baseline(wl.LLAMA3_8B, args.seed)
+        if enc is None:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference's encoder is not built here (oracle/build_ref.sh)"}))
+            return
+        print(json.dumps({"impl": "reference", "metric": "sidecar_build_melem_per_s", "value": enc["processes"]["value"],
+                          "unit": "M elements/s", "n_gpus": args.gpus, "higher_is_better": True, "dtype": "u16",
+                          "data": "synthetic", "config": {"workload": enc["what"], "cpu": cpu_model()},
+                          "cpu_baseline": {"value": enc["processes"]["value"], "unit": "M elements/s", "kind": "reference",
+                                           "cores": enc["processes"]["cores"], "sample": enc["processes"]["sample"]},
+                          "one_thread": enc["one_thread"],
+                          "e2e": {"value": enc["processes"]["value"], "unit": "M elements/s", "h2d_bytes_per_step": 0,
+                                  "d2h_bytes_per_step": 0}, "gpu_launches": 0}), flush=True)
+        return
     if args.workload != "model":
         return run_reference_cases(args, cores)
     cfg, tp, wname, layers = workload_for(args.gpus, args.layers)
@@ -815,6 +829,67 @@ def run_cases(args, local_rank):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------
+# the sidecar builder on its own (the offline half of the path)
+# ------------------------------------------------------------------------------------------------
+
+def run_build(args, local_rank):
+    """One gate/up-sized weight of the 8B-shaped model (14336 x 4096, per-channel scales) through
+    MPServe_cuda.huffman_build_fp8_decode_tables, inputs resident, artifacts left on the device."""
+    import MPServe_cuda
+    from mpserve_b200 import _lib
+
+    _lib.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    n, m = 14336, 4096
+    c = wl.quantize_fp8(wl.random_weight(n, m, args.seed, "normal", device=dev), "channel")
+
+    def step():
+        return MPServe_cuda.huffman_build_fp8_decode_tables(c.bf16, c.fp8_u8, c.scales_u16, max_len=7, threads_per_block=1024)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(args.warmup):
+        art = step()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(args.steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        art = step()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    clocks = sampler.stop()
+    out = MPServe_cuda.huffman_decode_fp8(c.fp8_u8, *[art[k] for k in DECODE_KEYS], n, m, 7)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.uint16), c.bf16.view(torch.uint16)), "the built sidecar does not decode to the source"
+    ms = float(np.median(times))
+    art_bytes = sum(v.numel() * v.element_size() for v in art.values() if isinstance(v, torch.Tensor))
+    alg = 3 * n * m + 2 * c.scales_u16.numel() + art_bytes      # read BF16 + FP8 + scales once, write the artifacts once
+    peak, peak_src = hbm_peak()
+    cpu_baseline = None
+    if not args.no_cpu_baseline:
+        cpu_baseline = cpu_encode_baseline(wl.LLAMA3_8B, args.seed)
+    line = {
+        "metric": "sidecar_build_melem_per_s", "value": n * m / ms / 1e3, "unit": "M elements/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u16", "data": "synthetic",
+        "config": {"workload": f"sidecar build of one {n}x{m} weight, N(0,0.02), per-channel FP8-E4M3 scales, L=7, k=1024",
+                   "l2": "inputs and scratch of one build (hundreds of MB) exceed L2"},
+        "roofline": {"bound": "hbm", "achieved": alg / (ms / 1e3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": alg / (ms / 1e3) / 1e9 / peak, "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_launch": alg, "kernel_ms": ms,
+                     "note": "a build is some forty launches and three host synchronisations; the time is that of the whole call"},
+        "cpu_baseline": cpu_baseline,
+        "artifact_bytes": art_bytes, "tables": int(art["decode_syms_u16"].shape[0]), "buckets": int(art["bucket_table_i32"].shape[0]),
+        "gpu_launches": None,
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_reference_cases(args, cores):
     """CPU port on the first case of the workload (FP8 workloads), a bounded number of repetitions per step."""
     from oracle import oracle as orc
@@ -850,7 +925,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="model", choices=["model", "single", "sizes", "awq"])
+    ap.add_argument("--workload", default="model", choices=["model", "single", "sizes", "awq", "build"])
     ap.add_argument("--layers", type=int, default=None, help="shorten the model to this many layers (quicker)")
     ap.add_argument("--k", type=int, default=None, help="sub-streams per bucket for the single-tensor workloads")
     ap.add_argument("--max-bytes", type=int, default=1 << 30, help="largest BF16 output of --workload sizes")
@@ -865,6 +940,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "build":
+        if rank == 0:
+            run_build(args, local_rank)
         return
     if args.workload != "model":
         if rank == 0:

@@ -52,6 +52,10 @@ struct BuildState {
     int64_t num_scales, num_chunks;
     size_t o_sh_keep;          // start of what the layout call leaves for the emit call
     size_t o_sh_end;           // end of it
+    // rectangular buckets: what the layout call leaves in the scratch area for the emit call
+    size_t o_rect_codes;       // uint32 [numel] code of every element, in bucket order (see rect_codes_kernel)
+    size_t o_rect_ebase;       // uint64 [B+1]   first element of every bucket in that order
+    int64_t rect_buckets;      // B of the layout call (0: no layout yet)
 };
 static_assert(sizeof(BuildState) <= 256, "mps_build_state is 256 bytes");
 
@@ -424,10 +428,144 @@ __device__ __forceinline__ int element_code(const CodeBook& cb, int gid, uint32_
     return len + (raw ? 16 : 0);
 }
 
+// elements of every bucket (rows x columns), [B] = 0 for the scan that follows
+__global__ void bucket_totals_kernel(RectGeom g, unsigned long long* __restrict__ totals) {
+    for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b <= g.B; b += (long long)gridDim.x * blockDim.x) {
+        unsigned long long t = 0;
+        if (b < g.B) t = (unsigned long long)(g.row_ofs[b + 1] - g.row_ofs[b]) * (unsigned long long)(g.group_col ? g.group_size : g.col_len[b]);
+        totals[b] = t;
+    }
+}
+
+// The code of every element, looked up once, in parallel, and stored in bucket order (element e of
+// bucket b at ebase[b] + e), so that the two walks over the sub-streams (sizes, then bits) read their
+// elements t, t + k, ... as coalesced words instead of searching a codebook per element.
+// An entry is len << 16 | code, bit 31 set when 16 raw bits follow (ESC); 0xFFFFFFFF: no code.
+// A CTA serves slabs of one bucket and first copies that bucket's codebooks (the symbols and codes of
+// its contexts, a few thousand items) into shared memory; a bucket with more items than fit is
+// searched in global memory instead.
+constexpr int kCodeCap = 6144;
+constexpr int kCodeSlab = 8192;
+constexpr uint32_t kNoCode = 0xFFFFFFFFu;
+__global__ void __launch_bounds__(256)
+rect_codes_kernel(RectGeom g, CodeBook cb, long long G, const unsigned long long* __restrict__ ebase, uint32_t* __restrict__ lc) {
+    __shared__ uint32_t s_ofs[257];
+    __shared__ int32_t s_gid[256];
+    __shared__ uint32_t s_esc[256];
+    __shared__ uint16_t s_escsym[256];
+    __shared__ uint32_t s_enc[kCodeCap];
+    __shared__ uint16_t s_sym[kCodeCap];
+    __shared__ uint32_t s_warp[8];
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const long long b = blockIdx.x;
+    const int row_a = g.row_ofs[b];
+    const unsigned long long nrows = (unsigned long long)(g.row_ofs[b + 1] - row_a);
+    const unsigned long long col_len = (unsigned long long)(g.group_col ? g.group_size : g.col_len[b]);
+    const long long col_start = g.group_col ? 0 : g.col_start[b];
+    const unsigned long long total = nrows * col_len;
+    const unsigned long long nslab = (total + kCodeSlab - 1) / kCodeSlab;
+    if (blockIdx.y >= nslab) return;
+
+    // this bucket's contexts: table id, items, ESC code
+    int32_t gid = -1;
+    uint32_t nd = 0;
+    if (tid < g.nctx) {
+        gid = g.bucket_table[b * g.nctx + tid];
+        if (gid >= G) gid = -1;
+        if (gid >= 0) nd = (uint32_t)(cb.ctx_ofs[gid + 1] - cb.ctx_ofs[gid]);
+    }
+    s_gid[tid] = gid;
+    s_esc[tid] = gid >= 0 ? cb.esc[gid] : 0u;
+    s_escsym[tid] = gid >= 0 ? cb.escsym[gid] : (uint16_t)0;
+    uint32_t incl = nd;   // inclusive prefix of nd over the CTA
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_warp[w] = incl;
+    __syncthreads();
+    uint32_t before = 0, items_total = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (i < w) before += s_warp[i];
+        items_total += s_warp[i];
+    }
+    s_ofs[tid] = before + incl - nd;
+    if (tid == 255) s_ofs[256] = items_total;
+    __syncthreads();
+    const bool staged = items_total <= (uint32_t)kCodeCap;
+    if (staged) {
+        for (uint32_t j = tid; j < items_total; j += 256) {
+            int lo = 0, hi = 256;   // last context whose items start at or before j
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (s_ofs[mid] <= j) lo = mid; else hi = mid;
+            }
+            const long long src = (long long)cb.ctx_ofs[s_gid[lo]] + (j - s_ofs[lo]);
+            s_sym[j] = (uint16_t)(cb.items[src] & 0xFFFF);
+            s_enc[j] = cb.enc[src];
+        }
+    }
+    __syncthreads();
+
+    // the code of one element
+    auto lookup = [&](uint32_t c, uint32_t sym) -> uint32_t {
+        const int32_t gd = s_gid[c];
+        if (gd < 0) return kNoCode;
+        if (staged) {
+            int lo = (int)s_ofs[c], hi = (int)s_ofs[c + 1] - 1;
+            while (lo <= hi) {
+                const int mid = (lo + hi) >> 1;
+                const uint32_t x = s_sym[mid];
+                if (x == sym) {
+                    uint32_t lcv = s_enc[mid];
+                    bool raw = false;
+                    if (lcv == 0) {                   // not in the codebook: the ESC code, then the raw 16 bits ...
+                        lcv = s_esc[c];
+                        raw = (sym != s_escsym[c]);   // ... unless the symbol is the synthetic ESC symbol itself
+                    }
+                    return lcv != 0 ? (lcv | (raw ? 0x80000000u : 0u)) : kNoCode;
+                }
+                if (x < sym) lo = mid + 1; else hi = mid - 1;
+            }
+            return kNoCode;
+        }
+        uint32_t code = 0; int len = 0; bool raw = false;
+        if (element_code(cb, gd, sym, code, len, raw) < 0) return kNoCode;
+        return ((uint32_t)len << 16) | code | (raw ? 0x80000000u : 0u);
+    };
+    uint32_t* out = lc + ebase[b];
+    constexpr int UN = 4;   // elements in flight per thread: their loads are issued before any is looked up
+    for (unsigned long long slab = blockIdx.y; slab < nslab; slab += gridDim.y) {
+        const unsigned long long e_end = (slab + 1) * kCodeSlab < total ? (slab + 1) * kCodeSlab : total;
+        unsigned long long e = slab * kCodeSlab + tid;
+        unsigned long long rr = e / col_len, cc = e - rr * col_len;   // one division per slab, then a running (row, column)
+        for (; e < e_end; e += 256 * UN) {
+            uint32_t c[UN], sy[UN];
+#pragma unroll
+            for (int u = 0; u < UN; ++u) {
+                while (cc >= col_len) { cc -= col_len; ++rr; }
+                if (e + 256ull * u < e_end) {
+                    const long long i = (long long)g.rows[row_a + rr] * g.m + (g.group_col ? g.group_col[row_a + rr] : col_start) + (long long)cc;
+                    c[u] = g.ctx[i] & g.ctx_mask;
+                    sy[u] = g.sym[i];
+                }
+                cc += 256;
+            }
+#pragma unroll
+            for (int u = 0; u < UN; ++u)
+                if (e + 256ull * u < e_end) out[e + 256ull * u] = lookup(c[u], sy[u]);
+        }
+    }
+}
+
+// One thread per sub-stream walks its elements t, t + k_eff, ...: the size of the sub-stream in bits,
+// or (EMIT) its bits written MSB-first, whole words with one 64-bit atomic OR each.
 template <bool EMIT>
-__global__ void rect_walk_kernel(RectGeom g, CodeBook cb, const uint32_t* __restrict__ startbit,
-                                 const long long* __restrict__ bit_base, uint32_t* __restrict__ bits_out,
-                                 unsigned long long* __restrict__ bitstream, int* __restrict__ err) {
+__global__ void rect_walk_kernel(RectGeom g, const unsigned long long* __restrict__ ebase, const uint32_t* __restrict__ lc,
+                                 const uint32_t* __restrict__ startbit, const long long* __restrict__ bit_base,
+                                 uint32_t* __restrict__ bits_out, unsigned long long* __restrict__ bitstream, int* __restrict__ err) {
     const long long total_threads = g.B * g.k;
     for (long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x; id < total_threads; id += (long long)gridDim.x * blockDim.x) {
         const long long b = id / g.k;
@@ -440,38 +578,47 @@ __global__ void rect_walk_kernel(RectGeom g, CodeBook cb, const uint32_t* __rest
         long long k_eff = total < 1 ? 1 : total;
         if (k_eff > g.k) k_eff = g.k;
         if (t >= k_eff) { if (!EMIT) bits_out[id] = 0; continue; }
-        const int32_t* bt = g.bucket_table + b * g.nctx;
-        // output cursor (emit)
-        long long w = 0; int fill = 0; unsigned long long acc = 0;
+        const uint32_t* codes = lc + ebase[b];
+        long long w = 0; int fill = 0; unsigned long long acc = 0;   // output cursor (emit)
         if (EMIT) {
             const long long bitpos = bit_base[b] + (long long)startbit[b * ((long long)g.k + 1) + t];
             w = bitpos >> 6; fill = (int)(bitpos & 63);
         }
         unsigned long long bits = 0;
-        long long rr = t / col_len, cc = t - rr * col_len;
-        for (long long e = t; e < total; e += k_eff) {
-            const long long i = (long long)g.rows[row_a + rr] * g.m + (g.group_col ? g.group_col[row_a + rr] : col_start) + cc;
-            const int gid = bt[g.ctx[i] & g.ctx_mask];
-            uint32_t code = 0; int len = 0; bool raw = false;
-            const uint32_t sym = g.sym[i];
-            const int nb = (gid >= 0) ? element_code(cb, gid, sym, code, len, raw) : -1;
-            if (nb < 0) { atomicExch(err, 3); break; }
+        constexpr int UN = 4;   // codes loaded ahead of their use
+        bool bad = false;
+        for (long long e0 = t; e0 < total && !bad; e0 += UN * k_eff) {
+          uint32_t ahead[UN];
+#pragma unroll
+          for (int u = 0; u < UN; ++u) ahead[u] = (e0 + u * k_eff < total) ? codes[e0 + u * k_eff] : 0u;
+#pragma unroll
+          for (int u = 0; u < UN; ++u) {
+            const long long e = e0 + u * k_eff;
+            if (e >= total) break;
+            const uint32_t v = ahead[u];
+            if (v == kNoCode) { atomicExch(err, 3); bad = true; break; }
+            const bool raw = (v >> 31) != 0;
+            const int nb = (int)((v >> 16) & 0x7FFFu) + (raw ? 16 : 0);
             bits += (unsigned long long)nb;
             if (EMIT) {
                 // the code, then (after an ESC) the 16 raw bits, MSB first
-                unsigned long long v = raw ? (((unsigned long long)code << 16) | sym) : code;
+                unsigned long long val = v & 0xFFFFu;
+                if (raw) {
+                    const long long rr = e / col_len, cc = e - rr * col_len;
+                    const long long i = (long long)g.rows[row_a + rr] * g.m + (g.group_col ? g.group_col[row_a + rr] : col_start) + cc;
+                    val = (val << 16) | g.sym[i];
+                }
                 int left = nb;
                 while (left > 0) {
                     const int room = 64 - fill;
                     const int take = left < room ? left : room;
-                    const unsigned long long part = (v >> (left - take)) & ((take >= 64) ? ~0ull : ((1ull << take) - 1ull));
+                    const unsigned long long part = (val >> (left - take)) & ((take >= 64) ? ~0ull : ((1ull << take) - 1ull));
                     acc |= part << (room - take);
                     fill += take; left -= take;
                     if (fill == 64) { atomicOr(&bitstream[w], acc); ++w; acc = 0; fill = 0; }
                 }
             }
-            cc += k_eff;
-            while (cc >= col_len) { cc -= col_len; ++rr; }
+          }
         }
         if (EMIT) { if (acc) atomicOr(&bitstream[w], acc); }
         else bits_out[id] = (uint32_t)bits;
@@ -838,14 +985,18 @@ int mps_build_analyze(mps_build_state* state, const uint16_t* bf16_bits, const u
     auto* chunk_seg = C.take<uint32_t>(num_chunks);
     auto* split_seg = C.take<uint32_t>(num_split);
     auto* dense = C.take<uint32_t>((size_t)num_split * 65536u);
+    auto* split_range = C.take<uint32_t>((size_t)num_split * 2);     // smallest, largest symbol of every split segment
     if (!C.ok()) { set_error("workspace too small"); return MPS_ERR_WORKSPACE; }
     hist::chunk_fill_kernel<<<grid_for(nseg), 256, 0, st>>>(seg_cnt, nseg, chunk_ofs, split_id, chunk_seg, split_seg);
-    if (num_split) MPS_CUDA_TRY(cudaMemsetAsync(dense, 0, (size_t)num_split * 65536u * sizeof(uint32_t), st));
+    if (num_split) {
+        MPS_CUDA_TRY(cudaMemsetAsync(dense, 0, (size_t)num_split * 65536u * sizeof(uint32_t), st));
+        hist::split_range_init_kernel<<<grid_for(num_split), 256, 0, st>>>(split_range, num_split);
+    }
     MPS_CUDA_TRY(cudaMemsetAsync(seg_cur, 0, (nseg + 1) * sizeof(uint32_t), st));
     if (num_chunks)
         hist::chunk_count_kernel<<<(unsigned)num_chunks, 256, 0, st>>>(seg_syms, seg_cnt, seg_ofs, chunk_seg, chunk_ofs, split_id, dense,
-                                                                       st_sym, st_cnt, seg_cur);
-    if (num_split) hist::split_finish_kernel<<<(unsigned)num_split, 256, 0, st>>>(split_seg, seg_ofs, dense, st_sym, st_cnt, seg_cur);
+                                                                       split_range, st_sym, st_cnt, seg_cur);
+    if (num_split) hist::split_finish_kernel<<<(unsigned)num_split, 256, 0, st>>>(split_seg, seg_ofs, dense, split_range, st_sym, st_cnt, seg_cur);
     need = kCubTempBytes;
     MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(cub_tmp, need, seg_cur, seg_cur, (int)(nseg + 1), st));
     hist::gather_items_kernel<<<grid_for(nseg * 32), 256, 0, st>>>(seg_cnt, seg_ofs, seg_cur, ctx_id, nseg, g.nctx, scale_of_rank, st_sym,
@@ -1003,11 +1154,33 @@ int mps_build_rect_layout(mps_build_state* state, const uint16_t* bf16_bits, con
     BuildState& S = *state_of(state);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     Carver C{S.ws, S.o_scratch, S.ws_bytes};
+    auto* codes = C.take<uint32_t>((size_t)S.numel);                      // kept for the emit call, with ...
+    auto* ebase = C.take<unsigned long long>(num_buckets + 1);            // ... the buckets' offsets into it
     auto* bits = C.take<uint32_t>((size_t)num_buckets * k);
     auto* bucket_bits = C.take<unsigned long long>(num_buckets + 1);
+    auto* totals = C.take<unsigned long long>(num_buckets + 1);
+    const size_t kScanTemp = 1 << 20;
+    void* scan_tmp = C.take<uint8_t>(kScanTemp);
     if (!C.ok()) { set_error("workspace too small for %lld buckets of %d sub-streams", (long long)num_buckets, k); return MPS_ERR_WORKSPACE; }
+    S.o_rect_codes = (uint8_t*)codes - S.ws; S.o_rect_ebase = (uint8_t*)ebase - S.ws; S.rect_buckets = 0;
     if (num_buckets > 0) {
-        rect_walk_kernel<false><<<grid_for(num_buckets * k), 256, 0, st>>>(g, cb, nullptr, nullptr, bits, nullptr, S.d_flag);
+        bucket_totals_kernel<<<grid_for(num_buckets + 1), 256, 0, st>>>(g, totals);
+        size_t need = 0;
+        MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(nullptr, need, totals, ebase, (int)(num_buckets + 1), st));
+        if (need > kScanTemp) { set_error("scan temporary storage exceeds the reserved %zu bytes", kScanTemp); return MPS_ERR_WORKSPACE; }
+        need = kScanTemp;
+        MPS_CUDA_TRY(cub::DeviceScan::ExclusiveSum(scan_tmp, need, totals, ebase, (int)(num_buckets + 1), st));
+        unsigned long long covered = 0;
+        MPS_CUDA_TRY(cudaMemcpyAsync(&covered, ebase + num_buckets, sizeof(covered), cudaMemcpyDeviceToHost, st));
+        MPS_CUDA_TRY(cudaStreamSynchronize(st));
+        if (covered > (unsigned long long)S.numel) { set_error("the buckets hold more elements than the tensor has"); return MPS_ERR_INVALID; }
+        // buckets of a weight are few and large, buckets of a grouped tensor many and small: eight CTAs
+        // share a large bucket's slabs, the spare ones of a small bucket leave at once
+        const unsigned split = (num_buckets >= 4096) ? 1u : 8u;
+        if (num_buckets > 0x7FFFFFFFLL) { set_error("too many buckets"); return MPS_ERR_INVALID; }
+        rect_codes_kernel<<<dim3((unsigned)num_buckets, split), 256, 0, st>>>(g, cb, S.G, ebase, codes);
+        S.rect_buckets = num_buckets;
+        rect_walk_kernel<false><<<grid_for(num_buckets * k), 256, 0, st>>>(g, ebase, codes, nullptr, nullptr, bits, nullptr, S.d_flag);
         rect_starts_kernel<<<grid_for(num_buckets, 64), 64, 0, st>>>(bits, bucket_row_offsets_i32, g.group_col ? nullptr : bucket_col_len_i32,
                                                                      g.group_size, num_buckets, k, bucket_thread_startbit_u32, bucket_bits);
     }
@@ -1036,10 +1209,13 @@ int mps_build_rect_emit(mps_build_state* state, const uint16_t* bf16_bits, const
     BuildState& S = *state_of(state);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (bitstream_words > 0) MPS_CUDA_TRY(cudaMemsetAsync(bitstream_u64, 0, (size_t)bitstream_words * 8, st));
-    if (num_buckets > 0)
+    if (num_buckets > 0) {
+        if (S.rect_buckets != num_buckets) { set_error("sidecar emit: call mps_build_rect_layout for the same buckets first"); return MPS_ERR_INVALID; }
         rect_walk_kernel<true><<<grid_for(num_buckets * k), 256, 0, st>>>(
-            g, cb, bucket_thread_startbit_u32, reinterpret_cast<const long long*>(bucket_bit_base_i64), nullptr,
+            g, reinterpret_cast<const unsigned long long*>(S.ws + S.o_rect_ebase), reinterpret_cast<const uint32_t*>(S.ws + S.o_rect_codes),
+            bucket_thread_startbit_u32, reinterpret_cast<const long long*>(bucket_bit_base_i64), nullptr,
             reinterpret_cast<unsigned long long*>(bitstream_u64), S.d_flag);
+    }
     MPS_CUDA_TRY(cudaGetLastError());
     return MPS_OK;
 }

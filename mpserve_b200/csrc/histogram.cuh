@@ -13,7 +13,8 @@
 //      value in shared memory in windows of kWindow symbol values starting at its smallest symbol (a
 //      context of a quantised weight sees a few dozen neighbouring BF16 patterns, so one window is
 //      the rule); segments longer than kChunk elements are split over several CTAs that add their
-//      windows into a dense 65536-counter array of that segment.
+//      windows into a dense 65536-counter array of that segment, of which the range between the
+//      segment's smallest and largest symbol is then read back.
 //
 // The result is what the sort-based formulation produced: items (scale << 32 | context << 16 | symbol)
 // in ascending order with their counts, and for every non-empty segment, in the same order, its first
@@ -28,7 +29,7 @@ namespace mps {
 namespace hist {
 
 constexpr int kScaleValues = 65536;
-constexpr int kChunk = 16384;       // elements of a segment counted by one CTA
+constexpr int kChunk = 65536;       // elements of a segment counted by one CTA
 constexpr int kWindow = 8192;       // symbol values counted at once
 constexpr int kWarpElems = 8192;    // elements a warp walks in the counting and scattering passes
 constexpr int kWalkWarps = 8;
@@ -157,6 +158,13 @@ __global__ void chunk_fill_kernel(const uint32_t* __restrict__ seg_cnt, long lon
     }
 }
 
+__global__ void split_range_init_kernel(uint32_t* __restrict__ split_range, long long num_split) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < num_split; i += (long long)gridDim.x * blockDim.x) {
+        split_range[2 * i] = 0xFFFFu;
+        split_range[2 * i + 1] = 0u;
+    }
+}
+
 // Exclusive prefix of `flag` over the CTA (256 threads) and the CTA's total.
 __device__ __forceinline__ uint32_t block_prefix(bool flag, uint32_t* s_warp, uint32_t& total) {
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -201,8 +209,8 @@ __device__ __forceinline__ uint32_t emit_nonzero(uint32_t range, uint32_t first,
 __global__ void __launch_bounds__(256)
 chunk_count_kernel(const uint16_t* __restrict__ seg_syms, const uint32_t* __restrict__ seg_cnt, const uint32_t* __restrict__ seg_ofs,
                    const uint32_t* __restrict__ chunk_seg, const uint32_t* __restrict__ chunk_ofs,
-                   const uint32_t* __restrict__ split_id, uint32_t* __restrict__ dense, uint16_t* __restrict__ st_sym,
-                   uint32_t* __restrict__ st_cnt, uint32_t* __restrict__ distinct) {
+                   const uint32_t* __restrict__ split_id, uint32_t* __restrict__ dense, uint32_t* __restrict__ split_range,
+                   uint16_t* __restrict__ st_sym, uint32_t* __restrict__ st_cnt, uint32_t* __restrict__ distinct) {
     __shared__ uint32_t s_count[kWindow];
     __shared__ uint32_t s_warp[8];
     __shared__ uint32_t s_lo, s_hi;
@@ -243,6 +251,10 @@ chunk_count_kernel(const uint16_t* __restrict__ seg_syms, const uint32_t* __rest
             uint32_t* mine = dense + (size_t)split_id[s] * 65536u + first;
             for (uint32_t d = threadIdx.x; d < range; d += 256)
                 if (s_count[d]) atomicAdd(&mine[d], s_count[d]);
+            if (threadIdx.x == 0 && first == lo) {   // the segment's symbol range, for split_finish_kernel
+                atomicMin(&split_range[2 * split_id[s]], lo);
+                atomicMax(&split_range[2 * split_id[s] + 1], hi);
+            }
         } else {
             written += emit_nonzero(range, first, [&](uint32_t d) { return s_count[d]; }, seg_ofs[s] + written, st_sym, st_cnt, s_warp);
         }
@@ -254,11 +266,13 @@ chunk_count_kernel(const uint16_t* __restrict__ seg_syms, const uint32_t* __rest
 // A split segment's dense counters -> its distinct symbols, ascending, with counts.
 __global__ void __launch_bounds__(256)
 split_finish_kernel(const uint32_t* __restrict__ split_seg, const uint32_t* __restrict__ seg_ofs, const uint32_t* __restrict__ dense,
-                    uint16_t* __restrict__ st_sym, uint32_t* __restrict__ st_cnt, uint32_t* __restrict__ distinct) {
+                    const uint32_t* __restrict__ split_range, uint16_t* __restrict__ st_sym, uint32_t* __restrict__ st_cnt,
+                    uint32_t* __restrict__ distinct) {
     __shared__ uint32_t s_warp[8];
     const uint32_t s = split_seg[blockIdx.x];
-    const uint32_t* mine = dense + (size_t)blockIdx.x * 65536u;
-    const uint32_t written = emit_nonzero(65536u, 0u, [&](uint32_t d) { return mine[d]; }, seg_ofs[s], st_sym, st_cnt, s_warp);
+    const uint32_t lo = split_range[2 * blockIdx.x], hi = split_range[2 * blockIdx.x + 1];   // the chunks' smallest and largest symbol
+    const uint32_t* mine = dense + (size_t)blockIdx.x * 65536u + lo;
+    const uint32_t written = emit_nonzero(hi - lo + 1u, lo, [&](uint32_t d) { return mine[d]; }, seg_ofs[s], st_sym, st_cnt, s_warp);
     if (threadIdx.x == 0) distinct[s] = written;
 }
 
