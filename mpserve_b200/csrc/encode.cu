@@ -88,6 +88,13 @@ __global__ void gather_u32_kernel(const uint32_t* __restrict__ src, const int* _
         dst[j] = src[idx[j]];
 }
 
+// SM count of the current device (148 on B200)
+static int sm_count_host() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+    return n;
+}
+
 static int grid_for(long long n, int threads = 256) {
     long long b = (n + threads - 1) / threads;
     if (b > 148LL * 32) b = 148LL * 32;
@@ -496,15 +503,33 @@ rect_codes_kernel(RectGeom g, CodeBook cb, long long G, const unsigned long long
     __syncthreads();
     const bool staged = items_total <= (uint32_t)kCodeCap;
     if (staged) {
-        for (uint32_t j = tid; j < items_total; j += 256) {
-            int lo = 0, hi = 256;   // last context whose items start at or before j
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (s_ofs[mid] <= j) lo = mid; else hi = mid;
+        // first item of every context, then four copies in flight per thread
+        __shared__ int s_first[256];
+        s_first[tid] = gid >= 0 ? cb.ctx_ofs[gid] : 0;
+        __syncthreads();
+        constexpr int SUN = 4;
+        for (uint32_t j0 = tid; j0 < items_total; j0 += 256 * SUN) {
+            long long src[SUN];
+#pragma unroll
+            for (int u = 0; u < SUN; ++u) {
+                const uint32_t j = j0 + 256u * u;
+                int lo = 0, hi = 256;   // last context whose items start at or before j
+                while (hi - lo > 1) {
+                    const int mid = (lo + hi) >> 1;
+                    if (s_ofs[mid] <= j) lo = mid; else hi = mid;
+                }
+                src[u] = (j < items_total) ? (long long)s_first[lo] + (j - s_ofs[lo]) : -1;
             }
-            const long long src = (long long)cb.ctx_ofs[s_gid[lo]] + (j - s_ofs[lo]);
-            s_sym[j] = (uint16_t)(cb.items[src] & 0xFFFF);
-            s_enc[j] = cb.enc[src];
+            unsigned long long it[SUN];
+            uint32_t en[SUN];
+#pragma unroll
+            for (int u = 0; u < SUN; ++u) {
+                it[u] = src[u] >= 0 ? cb.items[src[u]] : 0ull;
+                en[u] = src[u] >= 0 ? cb.enc[src[u]] : 0u;
+            }
+#pragma unroll
+            for (int u = 0; u < SUN; ++u)
+                if (src[u] >= 0) { s_sym[j0 + 256u * u] = (uint16_t)(it[u] & 0xFFFF); s_enc[j0 + 256u * u] = en[u]; }
         }
     }
     __syncthreads();
@@ -1174,9 +1199,11 @@ int mps_build_rect_layout(mps_build_state* state, const uint16_t* bf16_bits, con
         MPS_CUDA_TRY(cudaMemcpyAsync(&covered, ebase + num_buckets, sizeof(covered), cudaMemcpyDeviceToHost, st));
         MPS_CUDA_TRY(cudaStreamSynchronize(st));
         if (covered > (unsigned long long)S.numel) { set_error("the buckets hold more elements than the tensor has"); return MPS_ERR_INVALID; }
-        // buckets of a weight are few and large, buckets of a grouped tensor many and small: eight CTAs
-        // share a large bucket's slabs, the spare ones of a small bucket leave at once
-        const unsigned split = (num_buckets >= 4096) ? 1u : 8u;
+        // buckets of a weight are few and large, buckets of a grouped tensor many and small: as many CTAs
+        // share a bucket's slabs as it takes to fill the GPU once (every one of them stages the bucket's
+        // codebooks), the spare ones of a small bucket leave at once
+        long long share = (5LL * sm_count_host()) / num_buckets;   // about five CTAs of this kernel fit an SM
+        const unsigned split = (unsigned)(share < 1 ? 1 : (share > 32 ? 32 : share));
         if (num_buckets > 0x7FFFFFFFLL) { set_error("too many buckets"); return MPS_ERR_INVALID; }
         rect_codes_kernel<<<dim3((unsigned)num_buckets, split), 256, 0, st>>>(g, cb, S.G, ebase, codes);
         S.rect_buckets = num_buckets;

@@ -77,15 +77,32 @@ __global__ void unit_scatter_kernel(Geom g, const uint16_t* __restrict__ scales,
         unit_sorted[atomicAdd(&unit_cur[unit_scale(g, scales, u)], 1u)] = (uint32_t)u;
 }
 
-// Calls f(element index) for every element of unit u, lanes striding along rows.
-template <class F>
-__device__ __forceinline__ void for_unit_elements(const Geom& g, long long u, int lane, F&& f) {
+// Calls f(context, symbol) for every element of unit u, lanes striding along rows, four elements of a
+// lane loaded before any is handed on (so that four loads are in flight per lane, not one).
+template <bool WITH_SYM, class F>
+__device__ __forceinline__ void for_unit_elements(const Geom& g, long long u, int lane, const uint8_t* __restrict__ ctx,
+                                                  const uint16_t* __restrict__ sym, F&& f) {
     const long long bi = u / g.nbu1, bj = u - bi * g.nbu1;
     const long long r0 = bi * g.ub0, c0 = bj * g.ub1;
     const long long r1 = (r0 + g.ub0 < g.n) ? r0 + g.ub0 : g.n;
     const long long c1 = (c0 + g.ub1 < g.m) ? c0 + g.ub1 : g.m;
-    for (long long r = r0; r < r1; ++r)
-        for (long long c = c0 + lane; c < c1; c += 32) f(r * g.m + c);
+    constexpr int UN = 4;
+    for (long long r = r0; r < r1; ++r) {
+        const uint8_t* crow = ctx + r * g.m;
+        const uint16_t* srow = sym + r * g.m;
+        for (long long c = c0 + lane; c < c1; c += 32 * UN) {
+            uint32_t cv[UN], sv[UN];
+#pragma unroll
+            for (int k = 0; k < UN; ++k) {
+                const long long cc = c + 32 * k;
+                cv[k] = (cc < c1) ? crow[cc] : 0u;
+                if (WITH_SYM) sv[k] = (cc < c1) ? srow[cc] : 0u; else sv[k] = 0u;
+            }
+#pragma unroll
+            for (int k = 0; k < UN; ++k)
+                if (c + 32 * k < c1) f(cv[k] & g.ctx_mask, sv[k]);
+        }
+    }
 }
 
 // Pass 1 (SCATTER = false): sizes of the segments.  Pass 2 (SCATTER = true): symbols into segments;
@@ -113,7 +130,7 @@ segment_walk_kernel(Geom g, const uint16_t* __restrict__ sym, const uint8_t* __r
         for (int c = lane; c < g.nctx; c += 32) cnt[c] = 0;
         __syncwarp();
         for (long long uu = j; uu < j2; ++uu)
-            for_unit_elements(g, unit_sorted[uu], lane, [&](long long i) { atomicAdd(&cnt[ctx[i] & g.ctx_mask], 1u); });
+            for_unit_elements<false>(g, unit_sorted[uu], lane, ctx, sym, [&](uint32_t c, uint32_t) { atomicAdd(&cnt[c], 1u); });
         __syncwarp();
         if constexpr (!SCATTER) {
             for (int c = lane; c < g.nctx; c += 32)
@@ -125,9 +142,8 @@ segment_walk_kernel(Geom g, const uint16_t* __restrict__ sym, const uint8_t* __r
             }
             __syncwarp();
             for (long long uu = j; uu < j2; ++uu)
-                for_unit_elements(g, unit_sorted[uu], lane, [&](long long i) {
-                    const uint32_t c = ctx[i] & g.ctx_mask;
-                    seg_syms[base[c] + atomicAdd(&cnt[c], 1u)] = sym[i];
+                for_unit_elements<true>(g, unit_sorted[uu], lane, ctx, sym, [&](uint32_t c, uint32_t v) {
+                    seg_syms[base[c] + atomicAdd(&cnt[c], 1u)] = (uint16_t)v;
                 });
         }
         __syncwarp();
