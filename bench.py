@@ -48,7 +48,7 @@ UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch divided by its elements, from the ncu
 # capture summarised in profiles/ (traffic grows in proportion to the elements of a launch)
-NCU_TRAFFIC_BYTES_PER_ELEMENT = 3.757
+NCU_TRAFFIC_BYTES_PER_ELEMENT = 3.942
 E2E_MAX_PINNED_BYTES = 24 << 30   # pinned host memory one rank may take for the end-to-end leg, at most
 E2E_PINNED_SHARE = 0.35           # ... and all ranks of the box together this share of the memory that is free
 
