@@ -916,7 +916,37 @@ def run_reference_cases(args, cores):
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": "the headline case once per step, all host threads"},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    line["reference_cuda_kernel"] = reference_cuda_timing(c, art, n, m, max(5, args.steps))
     print(json.dumps(line), flush=True)
+
+
+def reference_cuda_timing(c, art_host, n, m, reps):
+    """The reference's own CUDA decode kernel (kernel/decode_huffman.cu, unmodified, built under oracle/_ref)
+    on the same sidecar, where a GPU is present and the kernel handles the sidecar (no ESC tables, no bitstream
+    of 3072..10240 words, no bucket narrower than its sub-stream count): for context beside the CPU number."""
+    from oracle import ref_decoder as refdec
+
+    if not torch.cuda.is_available():
+        return {"unavailable": "no GPU"}
+    if not refdec.available():
+        return {"unavailable": "oracle/_ref holds no build of the reference decoder (oracle/build_ref_decode.sh)"}
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    art = {k: torch.from_numpy(v).to(dev) for k, v in art_host.items() if isinstance(v, np.ndarray)}
+    why = refdec.refusal(art, n, m)
+    if why is not None:
+        return {"unavailable": f"not given to the reference kernel: {why}"}
+    ctx = c.fp8_u8.to(dev)
+    args_ = [art[k] for k in refdec.ORDER]
+    mod = refdec.module()
+    out = mod.huffman_decode_fp8(ctx, *args_, n, m, 7)
+    torch.cuda.synchronize()
+    if not torch.equal(out.view(torch.uint16), c.bf16.to(dev).view(torch.uint16)):
+        return {"unavailable": "the reference kernel's output differs from the source tensor"}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    med, best = _time_calls(lambda: mod.huffman_decode_fp8(ctx, *args_, n, m, 7), flush, reps)
+    return {"ms_median": med, "ms_best": best, "bf16_gbps": 2 * n * m / med / 1e6,
+            "what": "huffman_decode_fp8_entry of kernel/decode_huffman.cu:591-758 built for sm_100a, one call per step, "
+                    "L2 flushed before every call, CUDA events"}
 
 
 def main():
