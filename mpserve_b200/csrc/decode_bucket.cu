@@ -727,8 +727,9 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
                 const uint16_t* sp = T.decode_syms + (long long)gid * TS + j0;
                 const uint8_t* lp = T.decode_lens + (long long)gid * (TS / 2) + (j0 >> 1);
                 if (aligned) {
-                    sv[q] = __ldg(reinterpret_cast<const uint4*>(sp));
-                    lv[q] = __ldg(reinterpret_cast<const uint32_t*>(lp));
+                    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(sv[q].x), "=r"(sv[q].y), "=r"(sv[q].z), "=r"(sv[q].w) : "l"(sp));
+                    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(lv[q]) : "l"(lp));
                 } else {
                     sv[q].x = (uint32_t)sp[0] | ((uint32_t)sp[1] << 16);
                     sv[q].y = (uint32_t)sp[2] | ((uint32_t)sp[3] << 16);
