@@ -86,8 +86,8 @@ struct Smem {
     int32_t gid[256];                            // context -> table id of the staged tables
     int32_t gid_next[256];                       // same for the prepared item (written by the scout once the
                                                  // decoding warps have taken the previous contents)
-    int staged_tensor;
     int abort;                                   // a bounded wait gave up
+    unsigned long long tab_bar;                  // the raw tables of the item have landed (bulk copy into the table's own space)
     uint32_t armed;                              // blocks of steps the producer has armed so far (abort path)
     uint32_t zero;                               // always 0; read back to tie an instruction to values it must wait for
 };
@@ -695,6 +695,47 @@ __device__ void decode_generic(const Smem& sm, const uint32_t* rowbase, const mp
     }
 }
 
+// Eight fused entries from eight raw symbols and their eight packed length nibbles; returns whether any is an ESC.
+template <int L>
+__device__ __forceinline__ bool fuse_group(const uint4& sv, uint32_t lv, uint32_t (&ent)[8]) {
+    const uint32_t s[4] = {sv.x, sv.y, sv.z, sv.w};
+    bool esc = false;
+    if constexpr (L == 7) {
+        // nibbles i and i+4 of the eight, each alone in a 16-bit lane; one byte permute then
+        // glues a symbol's two bytes above its nibble
+        const uint32_t t = lv;
+        esc = (t & 0x88888888u) != 0u;
+        const uint32_t z[4] = {t & 0x000F000Fu, (t >> 4) & 0x000F000Fu, (t >> 8) & 0x000F000Fu, (t >> 12) & 0x000F000Fu};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            // bytes: [nibble, 0, sym.lo, sym.hi]; operand a = z (bytes 0-3), b = syms (bytes 4-7)
+            const uint32_t sel = ((i & 1) ? 0x7600u : 0x5400u) | ((i & 4) ? 0x32u : 0x10u);
+            ent[i] = __byte_perm(z[i & 3], s[i >> 1], sel);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t sym = (s[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+            const uint32_t nib = (lv >> (4 * i)) & 0xFu;
+            const uint32_t e = (nib == 15u);            // nibble 15 = ESC with an L-bit code
+            const uint32_t len = e ? (uint32_t)L : nib;
+            esc |= (e != 0);
+            ent[i] = (sym << 16) | (e << 15) | len;
+        }
+    }
+    return esc;
+}
+
+// The eight entries of a context without a table: the FP8 decoder emits zeros and consumes nothing
+// (decode_huffman.cu:252-264); the AWQ decoders treat it as an ESC (:476-485).  Returns whether that is an ESC.
+template <int L>
+__device__ __forceinline__ bool fill_group(uint32_t (&ent)[8]) {
+    const uint32_t fill = (L == 7) ? 0u : ((uint32_t)L | Entry<L>::kEsc);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ent[i] = fill;
+    return L != 7;
+}
+
 // Fuse the bucket's tables into shared memory; returns whether any entry is an ESC.
 // The raw tables of a bucket (up to 80 KB) usually come straight from HBM, so every thread first
 // issues a whole batch of independent 16-byte + 4-byte loads and only then converts them: the batch,
@@ -745,41 +786,9 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
             const int g = tid + (it0 + q) * THREADS;
             const int ctx = g / GROUPS_PER_CTX;
             const int j0 = (g - ctx * GROUPS_PER_CTX) * 8;
-            const uint32_t s[4] = {sv[q].x, sv[q].y, sv[q].z, sv[q].w};
             uint32_t ent[8];
-            if (gv[q] >= 0) {
-                if constexpr (L == 7) {
-                    // nibbles i and i+4 of the eight, each alone in a 16-bit lane; one byte permute then
-                    // glues a symbol's two bytes above its nibble
-                    const uint32_t t = lv[q];
-                    esc |= (t & 0x88888888u) != 0u;
-                    const uint32_t z[4] = {t & 0x000F000Fu, (t >> 4) & 0x000F000Fu, (t >> 8) & 0x000F000Fu,
-                                           (t >> 12) & 0x000F000Fu};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        // bytes: [nibble, 0, sym.lo, sym.hi]; operand a = z (bytes 0-3), b = syms (bytes 4-7)
-                        const uint32_t sel = ((i & 1) ? 0x7600u : 0x5400u) | ((i & 4) ? 0x32u : 0x10u);
-                        ent[i] = __byte_perm(z[i & 3], s[i >> 1], sel);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint32_t sym = (s[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
-                        const uint32_t nib = (lv[q] >> (4 * i)) & 0xFu;
-                        const uint32_t e = (nib == 15u);            // nibble 15 = ESC with an L-bit code
-                        const uint32_t len = e ? (uint32_t)L : nib;
-                        esc |= (e != 0);
-                        ent[i] = (sym << 16) | (e << 15) | len;
-                    }
-                }
-            } else {
-                // no table for this context: the FP8 decoder emits zeros and consumes nothing
-                // (decode_huffman.cu:252-264); the AWQ decoders treat it as an ESC (:476-485).
-                const uint32_t fill = (L == 7) ? 0u : ((uint32_t)L | Entry<L>::kEsc);
-                esc |= (L != 7);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) ent[i] = fill;
-            }
+            if (gv[q] >= 0) esc |= fuse_group<L>(sv[q], lv[q], ent);
+            else esc |= fill_group<L>(ent);
             uint4* dst = reinterpret_cast<uint4*>(&sm.tbl[ctx * TS + j0]);
             dst[0] = make_uint4(ent[0], ent[1], ent[2], ent[3]);
             dst[1] = make_uint4(ent[4], ent[5], ent[6], ent[7]);
@@ -788,9 +797,78 @@ __device__ __forceinline__ bool stage_tables(Smem& sm, const mps_bucket_tensor& 
     return group_or(esc ? 1 : 0, THREADS) != 0;
 }
 
+// The same fusion when the bucket's tables are one run of consecutive table ids (what the reference encoder
+// writes: tables are numbered by (scale, context), so the tables of one scale follow each other).  The
+// producer warp has then copied the raw run with two bulk copies into the upper end of the table's own
+// space -- symbols of the U tables at [end - 2.5 TS U, end - 0.5 TS U), packed lengths above them -- and
+// the decoding warps expand it in place: no load instruction, no address arithmetic per load, no trip
+// through the L1 for 80 KB per bucket.  Two waves of half the contexts each, lower half first; in a wave
+// every thread reads the raw groups of its share, all threads meet, then every thread writes its fused
+// groups.  The lower wave writes bytes [0, end/2), which hold raw symbols only of ranks below
+// 1.25 U - NCTX; those belong to contexts below U/4, which that same wave has read before it writes.  The
+// upper wave has read everything that is left before it writes anywhere.
+// Returns 1 if any entry is an ESC, 0 if none, -1 if the copy never landed (bounded wait).
+template <int L, int THREADS, typename F>
+__device__ __forceinline__ int stage_tables_inplace(Smem& sm, int tid, int32_t first, uint32_t count, uint32_t parity,
+                                                    uint32_t spin_limit, F&& after_issue) {
+    constexpr int TS = 1 << L;
+    constexpr int GROUPS_PER_CTX = TS / 8;
+    constexpr int NGROUPS = kTableEntries / 8;
+    constexpr int PER_WAVE = NGROUPS / 2 / THREADS;   // groups of 8 entries per thread and wave
+    static_assert(NGROUPS % (2 * THREADS) == 0 && PER_WAVE <= 8, "a wave's raw groups must fit a thread's registers");
+    after_issue();
+    if (!mbar_wait(smem_u32(&sm.tab_bar), parity, spin_limit)) return -1;
+    const uint32_t tbl = smem_u32(sm.tbl);
+    const uint32_t raw_syms = tbl + (uint32_t)kTableEntries * 4u - (uint32_t)(TS * 2 + TS / 2) * count;
+    const uint32_t raw_lens = tbl + (uint32_t)kTableEntries * 4u - (uint32_t)(TS / 2) * count;
+    bool esc = false;
+#pragma unroll
+    for (int wave = 0; wave < 2; ++wave) {
+        uint4 sv[PER_WAVE];
+        uint32_t lv[PER_WAVE];
+#pragma unroll
+        for (int q = 0; q < PER_WAVE; ++q) {
+            const int g = wave * (NGROUPS / 2) + tid + q * THREADS;
+            const int ctx = g / GROUPS_PER_CTX;
+            const int j0 = (g - ctx * GROUPS_PER_CTX) * 8;
+            const int32_t gid = sm.gid[ctx];
+            sv[q] = make_uint4(0u, 0u, 0u, 0u);
+            lv[q] = 0u;
+            if (gid >= 0) {
+                const uint32_t e0 = (uint32_t)(gid - first) * (uint32_t)TS + (uint32_t)j0;   // first entry of the group in the raw run
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(sv[q].x), "=r"(sv[q].y), "=r"(sv[q].z), "=r"(sv[q].w) : "r"(raw_syms + e0 * 2u) : "memory");
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(lv[q]) : "r"(raw_lens + (e0 >> 1)) : "memory");
+            }
+        }
+        group_sync(THREADS);   // every raw byte this wave may overwrite has been read
+#pragma unroll
+        for (int q = 0; q < PER_WAVE; ++q) {
+            const int g = wave * (NGROUPS / 2) + tid + q * THREADS;
+            const int ctx = g / GROUPS_PER_CTX;
+            const int j0 = (g - ctx * GROUPS_PER_CTX) * 8;
+            uint32_t ent[8];
+            if (sm.gid[ctx] >= 0) esc |= fuse_group<L>(sv[q], lv[q], ent);
+            else esc |= fill_group<L>(ent);
+            uint4* dst = reinterpret_cast<uint4*>(&sm.tbl[ctx * TS + j0]);
+            dst[0] = make_uint4(ent[0], ent[1], ent[2], ent[3]);
+            dst[1] = make_uint4(ent[4], ent[5], ent[6], ent[7]);
+        }
+    }
+    return group_or(esc ? 1 : 0, THREADS) != 0 ? 1 : 0;
+}
+
+// What the scout warp remembers between items: the context -> table map that is staged once the item
+// it prepared last has been decoded (lane i holds contexts i, i + 32, ...).
+template <int L>
+struct ScoutMemo {
+    int valid = 0, ti = -1;
+    int32_t gids[((L == 7 ? 256 : 16) + 31) / 32];
+};
+
 template <int L, int THREADS, int CH>
 __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws, int slot,
-                              int wait_iter, int& q_cur, int& q_end) {
+                              int wait_iter, int& q_cur, int& q_end, ScoutMemo<L>& memo) {
     constexpr int NCTX = (L == 7) ? 256 : 16;
     constexpr int TS = 1 << L;
     constexpr uint32_t SPAN = THREADS * CH;
@@ -911,17 +989,44 @@ __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws,
     // warp arrives on barrier 2 once per item, this warp joins it once per item it prepares during another
     // item (a hardware barrier: the waiting warp issues nothing while it waits).
     if (wait_iter >= 0) asm volatile("bar.sync 2, 64;" ::: "memory");
+    int restage = 0, dense = 0, first = 0;
+    uint32_t count = 0;
     if (ok) {
 #pragma unroll
         for (int j = 0; j < (NCTX + 31) / 32; ++j) {
             const int c = lane + 32 * j;
             if (c < NCTX) sm.gid_next[c] = gids[j];
         }
+        // does the item need other tables than the one before it, and are its tables one run of ids?
+        int differs = !memo.valid || memo.ti != ti;
+        int lowest = 0x7FFFFFFF;
+#pragma unroll
+        for (int j = 0; j < (NCTX + 31) / 32; ++j) {
+            differs |= (gids[j] != memo.gids[j]);
+            if (gids[j] >= 0 && gids[j] < lowest) lowest = gids[j];
+        }
+        restage = __any_sync(0xFFFFFFFFu, differs);
+        lowest = __reduce_min_sync(0xFFFFFFFFu, lowest);
+        int run = 1;
+#pragma unroll
+        for (int j = 0; j < (NCTX + 31) / 32; ++j) {   // contexts 32 j + lane: consecutive contexts are consecutive lanes
+            const uint32_t has = __ballot_sync(0xFFFFFFFFu, gids[j] >= 0);
+            const uint32_t rank = count + __popc(has & ((1u << lane) - 1u));
+            if (gids[j] >= 0 && gids[j] != lowest + (int)rank) run = 0;
+            count += __popc(has);
+        }
+        dense = __all_sync(0xFFFFFFFFu, run) && count > 0;
+        first = lowest;
+        memo.valid = 1; memo.ti = ti;
+#pragma unroll
+        for (int j = 0; j < (NCTX + 31) / 32; ++j) memo.gids[j] = gids[j];
     }
     if (lane == 0) {
+        P.restage = (int16_t)restage; P.tab_dense = (int16_t)dense; P.tab_first = first; P.tab_count = count;
         P.valid = 1; P.ok = ok ? 1 : 0; P.ti = ti; P.mode = mode;
         P.k = k; P.k_eff = k_eff; P.t_begin = t_begin; P.ebits = ebits;
-        P.b = b; P.row_a = row_a; P.nrows = nrows; P.col_start = col_start; P.col_len = col_len; P.total = total; P.wb = wb;
+        P.b = b; P.row_a = (int32_t)row_a; P.nrows = (int32_t)nrows; P.col_start = (int32_t)col_start; P.col_len = (int32_t)col_len;
+        P.total = total; P.wb = wb;
         P.rows_ok = rows_ok; P.rows_vec = rows_vec; P.rows_al16 = rows_al16;
         P.bit_lo = (uint32_t)(bit_base & 63);
     }
@@ -942,7 +1047,6 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
     const bool is_scout = tid >= THREADS + 32;       // the whole scout warp
 
     if (tid == 0) {
-        sm.staged_tensor = -1;
         sm.abort = 0;
         sm.armed = 0;
         sm.zero = 0;
@@ -950,6 +1054,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             mbar_init(smem_u32(&sm.full_bar[i]), 1u + kSS);  // lane 0's expect_tx + one arrive per step offset
             mbar_init(smem_u32(&sm.empty_bar[i]), THREADS / 32);
         }
+        mbar_init(smem_u32(&sm.tab_bar), 1u);                // the producer's expect_tx
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -957,18 +1062,21 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
     int q_cur = 0, q_end = 0;  // the scout's current grab from the work queue
     const uint32_t spin_limit = args.spin_limit ? args.spin_limit : kSpinLimit;
     const int stall_block = args.stall_block_plus1 - 1;
-    if (is_scout) scout_prepare<L, THREADS, CH>(args, sm, ws, 0, -1, q_cur, q_end);
+    ScoutMemo<L> memo;
+    if (is_scout) scout_prepare<L, THREADS, CH>(args, sm, ws, 0, -1, q_cur, q_end, memo);
     __syncthreads();
 
     bool staged_esc = false;
     uint32_t blk = 0;  // blocks of steps streamed so far by this CTA (same value in every thread)
+    uint32_t tab_copies = 0;   // bulk copies of raw tables so far: the phase of tab_bar (same value in every thread)
+    bool tab_inflight = false; // the item just handled armed tab_bar (abort path)
     for (int iter = 0;; ++iter) {
         const int slot = iter & 1;
         const Prepared& P = sm.prep[slot];
         if (!P.valid) break;
         if (is_scout) {
             // next item's geometry, row bases and L2 prefetches, while the others decode this one
-            scout_prepare<L, THREADS, CH>(args, sm, ws, slot ^ 1, iter + 1, q_cur, q_end);
+            scout_prepare<L, THREADS, CH>(args, sm, ws, slot ^ 1, iter + 1, q_cur, q_end, memo);
         } else if (P.ok) {
             const int ti = P.ti, mode = P.mode;
             const mps_bucket_tensor& T = sm.tensor[slot];
@@ -1013,7 +1121,24 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             bool run_ok = true;
             uint32_t nblocks = 0;
             if (stream) nblocks = (it.nsteps + kSS - 1) / kSS;
+            // tables that are one run of table ids are copied raw by the bulk-copy engine and expanded in place
+            constexpr bool kInplaceFits = (kTableEntries / 8) % (2 * THREADS) == 0 && (kTableEntries / 8) / (2 * THREADS) <= 8;
+            const bool tab_bulk = kInplaceFits && P.restage && P.tab_dense &&
+                                  ((reinterpret_cast<uintptr_t>(T.decode_syms) | reinterpret_cast<uintptr_t>(T.decode_lens)) & 15u) == 0;
+            const uint32_t tab_parity = tab_copies & 1u;
+            tab_inflight = tab_bulk;
             if (is_producer) {
+                if (tab_bulk && tid == THREADS) {
+                    constexpr uint32_t TS = 1u << L;
+                    const uint32_t count = P.tab_count;
+                    const uint32_t end = smem_u32(sm.tbl) + (uint32_t)kTableEntries * 4u;
+                    const uint32_t bar = smem_u32(&sm.tab_bar);
+                    // the table's space was written by ordinary stores while the previous bucket was staged
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    mbar_expect_tx(bar, (TS * 2u + TS / 2u) * count);
+                    bulk_g2s(end - (TS * 2u + TS / 2u) * count, T.decode_syms + (long long)P.tab_first * TS, TS * 2u * count, bar);
+                    bulk_g2s(end - (TS / 2u) * count, T.decode_lens + (long long)P.tab_first * (TS / 2), (TS / 2u) * count, bar);
+                }
                 if (stream) {
                     if (!split && it.k_eff == SPAN && (it.col_len & 15u) == 0u) run_ok = producer_rows<SPAN>(sm, it, blk, nblocks, stall_block, spin_limit);
                     else run_ok = split ? producer_run<SPAN, true>(sm, it, blk, nblocks, stall_block, spin_limit)
@@ -1024,35 +1149,36 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                 // The first chunks of the bitstream are requested right after the first batch of table
                 // loads: both wait on memory, and the table loads are the ones the threads need first.
                 constexpr int CPT = (NCTX + THREADS - 1) / THREADS;  // contexts per thread
-                int differs = (sm.staged_tensor != ti);
-                int32_t my_gid[CPT];
-#pragma unroll
-                for (int i = 0; i < CPT; ++i) {
-                    const int c = tid + i * THREADS;
-                    my_gid[i] = -1;
-                    if (c < NCTX) {
-                        my_gid[i] = sm.gid_next[c];
-                        differs |= (my_gid[i] != sm.gid[c]);
-                    }
-                }
-                differs = group_or(differs, THREADS);
-                if (tid < 32) asm volatile("bar.arrive 2, 64;" ::: "memory");  // the scout may now overwrite gid_next
-                if (differs) {
+                auto begin = [&] { if (stream) stream_begin<L, THREADS, CH>(sm, it, st); };
+                if (P.restage) {   // (the scout compared this item's map with the one staged now)
 #pragma unroll
                     for (int i = 0; i < CPT; ++i) {
                         const int c = tid + i * THREADS;
-                        if (c < NCTX) sm.gid[c] = my_gid[i];
+                        if (c < NCTX) sm.gid[c] = sm.gid_next[c];
                     }
-                    if (tid == 0) sm.staged_tensor = ti;
                     group_sync(THREADS);
-                    staged_esc = stage_tables<L, THREADS>(sm, T, tid, [&] { if (stream) stream_begin<L, THREADS, CH>(sm, it, st); });
-                } else if (stream) {
-                    stream_begin<L, THREADS, CH>(sm, it, st);
+                }
+                if (tid < 32) asm volatile("bar.arrive 2, 64;" ::: "memory");  // the scout may now overwrite gid_next
+                if (P.restage) {
+                    bool expanded = false;
+                    if constexpr (kInplaceFits) {
+                        if (tab_bulk) {
+                            const int r = stage_tables_inplace<L, THREADS>(sm, tid, P.tab_first, P.tab_count, tab_parity, spin_limit, begin);
+                            if (r < 0) run_ok = false;
+                            staged_esc = r > 0;
+                            expanded = true;
+                        }
+                    }
+                    if (!expanded) staged_esc = stage_tables<L, THREADS>(sm, T, tid, begin);
+                } else {
+                    begin();
                 }
 
                 // ---- decode --------------------------------------------------------------------------
                 const uint32_t t0 = t_begin + (uint32_t)tid * CH;
-                if (stream) {
+                if (!run_ok) {
+                    // the raw tables never landed: the wait gave up, the CTA reports and stops below
+                } else if (stream) {
                     if (split)
                         run_ok = staged_esc ? stream_run<L, THREADS, CH, true, true>(sm, it, st, blk, spin_limit)
                                             : stream_run<L, THREADS, CH, false, true>(sm, it, st, blk, spin_limit);
@@ -1076,6 +1202,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             }
             if (!run_ok) sm.abort = 1;
             blk += nblocks;
+            tab_copies += tab_bulk ? 1u : 0u;
         }
         if (!P.ok && tid < 32) asm volatile("bar.arrive 2, 64;" ::: "memory");
         __syncthreads();  // item done: tables, rings and the other prepared slot may now be overwritten
@@ -1090,6 +1217,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
     if (sm.abort) {
         if (is_consumer) cp_async_wait<0>();
         if (tid == THREADS) {
+            if (tab_inflight) mbar_wait(smem_u32(&sm.tab_bar), (tab_copies - 1u) & 1u, spin_limit);
             constexpr uint32_t NST = ring_stages(SPAN);
             const uint32_t armed = sm.armed;
             for (uint32_t g = (armed > NST ? armed - NST : 0u); g < armed; ++g)

@@ -27,9 +27,15 @@ struct Prepared {
     int ok;     // geometry usable, else the item is skipped
     int ti, mode;
     uint32_t k, k_eff, t_begin, ebits;
-    long long b, row_a, nrows, col_start, col_len, total, wb;
+    long long b, total, wb;
+    int32_t row_a, nrows, col_start, col_len;   // (int32 in the sidecar)
     int rows_ok, rows_vec, rows_al16;
     uint32_t bit_lo;  // low six bits of the bucket's bit base (0 in every sidecar the reference encoder writes)
+    // tables: must they be staged (another context -> table map than the item decoded before), and are they
+    // one run of consecutive table ids in context order (the reference encoder numbers tables by (scale, context))
+    int16_t restage, tab_dense;
+    int32_t tab_first;   // table id of the first context that has one
+    uint32_t tab_count;  // contexts that have one
 };
 
 struct BitOrigin {        // bitstream of the item seen from a 16-byte aligned origin

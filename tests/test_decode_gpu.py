@@ -246,6 +246,38 @@ def test_fp8_argument_validation(dev):
         MPServe_cuda.huffman_decode_fp8(*bad)
 
 
+@pytest.mark.parametrize("cfg", [(256, 4), (256, 1)], ids=str)
+def test_fp8_tables_in_any_order(dev, force_config, cfg):
+    """The reference encoder numbers a bucket's tables consecutively in context order, which the decoder
+    uses (one bulk copy of the run, expanded in place); a sidecar whose tables are stored in another
+    order, or that shares a table between contexts, must decode just the same through the other path."""
+    n, m = 512, 4096
+    c = wl.quantize_fp8(wl.random_weight(n, m, 21, "normal"), "tensor")
+    art = orc.build_fp8(_u16(c.bf16), c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, 1024)
+    want = _u16(c.bf16)
+    force_config(*cfg)
+    np.testing.assert_array_equal(_fp8_decode(c.fp8_u8.numpy(), art, n, m, dev), want)
+    G = art["decode_syms_u16"].shape[0]
+    perm = np.random.default_rng(3).permutation(G)            # new position of every table
+    shuffled = dict(art)
+    shuffled["decode_syms_u16"] = np.empty_like(art["decode_syms_u16"])
+    shuffled["decode_lens_u8"] = np.empty_like(art["decode_lens_u8"])
+    shuffled["decode_syms_u16"][perm] = art["decode_syms_u16"]
+    shuffled["decode_lens_u8"][perm] = art["decode_lens_u8"]
+    bt = art["bucket_table_i32"].copy()
+    bt[bt >= 0] = perm[bt[bt >= 0]].astype(np.int32)
+    shuffled["bucket_table_i32"] = bt
+    np.testing.assert_array_equal(_fp8_decode(c.fp8_u8.numpy(), shuffled, n, m, dev), want)
+    # a run of consecutive ids that does not start at the first context's table: reversed order
+    rev = dict(art)
+    rev["decode_syms_u16"] = art["decode_syms_u16"][::-1].copy()
+    rev["decode_lens_u8"] = art["decode_lens_u8"][::-1].copy()
+    bt = art["bucket_table_i32"].copy()
+    bt[bt >= 0] = (G - 1 - bt[bt >= 0]).astype(np.int32)
+    rev["bucket_table_i32"] = bt
+    np.testing.assert_array_equal(_fp8_decode(c.fp8_u8.numpy(), rev, n, m, dev), want)
+
+
 def test_fp8_checked_arguments_are_remembered_but_rechecked_when_they_change(dev):
     """A second call with the same tensor objects skips the argument checks; a tensor changed in place
     between two calls (another dtype, another shape, other storage) is checked again in full."""
