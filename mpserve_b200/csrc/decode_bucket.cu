@@ -310,12 +310,17 @@ struct SChain {
 
 // Move by `used` (< 32) bits and return the fresh 32-bit window.  Branch-free: the register
 // rotation and the ring read are predicated on having moved into the next unit.
+// MASK: 60 for a sub-stream's own ring of 64 bytes; kFlatMask when the bucket's whole bitstream lies in
+// shared memory from `ring` on (every sub-stream then reads the same copy at its own position).
+constexpr uint32_t kFlatBytes = sizeof(uint4) * 4 * 1024;   // the space of the rings: 64 KB
+constexpr uint32_t kFlatMask = kFlatBytes - 4;
+template <uint32_t MASK = 60u>
 __device__ __forceinline__ uint32_t schain_window(SChain& ch, uint32_t ring, uint32_t used) {
     const uint32_t np = ch.pos + used;
     const uint32_t moved = np ^ ch.pos;
-    // byte address of unit (np >> 5) + 1 in the ring: units are 4 bytes, swapped in pairs (^4), ring of 64 bytes
+    // byte address of unit (np >> 5) + 1: units are 4 bytes, swapped in pairs (^4)
     uint32_t addr;
-    asm("lop3.b32 %0, %1, 4, 60, 0x28;" : "=r"(addr) : "r"((np >> 3) + 4u));  // (x ^ 4) & 60
+    asm("lop3.b32 %0, %1, 4, %2, 0x28;" : "=r"(addr) : "r"((np >> 3) + 4u), "n"(MASK));  // (x ^ 4) & MASK
     addr += ring;
     ch.pos = np;
     asm volatile(
@@ -493,6 +498,7 @@ __device__ __forceinline__ void stream_begin(Smem& sm, const StreamItem& it, Str
         st.ch[c].pos = pos;
         st.ch[c].next = (pos >> 7) + kRingChunks;
     }
+    if (it.flat_bytes) return;   // the whole bitstream comes with one bulk copy
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
 #pragma unroll
@@ -506,9 +512,13 @@ __device__ __forceinline__ void stream_begin(Smem& sm, const StreamItem& it, Str
     cp_async_commit();
 }
 
-template <int L, int THREADS, int CH, bool ESC, bool SPLIT>
+// FLAT: the bucket's bitstream was bulk-copied whole into the space of the rings (a bucket of up to 64 KB of
+// code bits: the attention projections, every shard of them): no first chunks to fetch, no requests in the loop.
+template <int L, int THREADS, int CH, bool ESC, bool SPLIT, bool FLAT = false>
 __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st,
-                                           uint32_t blk, uint32_t spin_limit) {
+                                           uint32_t blk, uint32_t bulk_parity, uint32_t spin_limit) {
+    static_assert(!(FLAT && SPLIT), "the resident-bitstream loop serves rows that hold whole steps");
+    constexpr uint32_t WMASK = FLAT ? kFlatMask : 60u;
     constexpr int RP = ESC ? 1 : ((32 - L) / L + 1);   // symbols per 32-bit window
     // Steps between bitstream requests: rare requests cost fewer instructions, frequent ones let
     // cp.async.wait_group leave more of them in flight, which is what a thread with few chains needs.
@@ -532,15 +542,26 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
     const uint32_t t0 = it.t_begin + tid * CH;
     const uint32_t zero = *reinterpret_cast<volatile uint32_t*>(&sm.zero);
 
-    // first units of every sub-stream (their chunks were requested in stream_begin by this warp's lanes)
-    cp_async_wait<0>();
-    __syncwarp();
+    // first units of every sub-stream (their chunks were requested in stream_begin by this warp's lanes, or the
+    // whole bitstream was copied by the producer warp)
+    const uint32_t flat0 = smem_u32(sm.bitring);
+    auto ring_of = [&](int c) { return FLAT ? flat0 : ring0 + c * THREADS * kRingBytes; };
+    if constexpr (FLAT) {
+        if (!mbar_wait(smem_u32(&sm.tab_bar), bulk_parity, spin_limit)) return false;
+    } else {
+        cp_async_wait<0>();
+        __syncwarp();
+    }
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-        const uint32_t ring = ring0 + c * THREADS * kRingBytes;
         const uint32_t u = st.ch[c].pos >> 5;
-        st.ch[c].w0 = lds_ordered(ring_unit_addr(ring, u));
-        st.ch[c].w1 = lds_ordered(ring_unit_addr(ring, u + 1));
+        if constexpr (FLAT) {
+            st.ch[c].w0 = lds_ordered(flat0 + (((u ^ 1u) << 2) & kFlatMask));
+            st.ch[c].w1 = lds_ordered(flat0 + ((((u + 1u) ^ 1u) << 2) & kFlatMask));
+        } else {
+            st.ch[c].w0 = lds_ordered(ring_unit_addr(ring_of(c), u));
+            st.ch[c].w1 = lds_ordered(ring_unit_addr(ring_of(c), u + 1));
+        }
     }
 
     uint32_t hi[CH], acc[CH];
@@ -605,7 +626,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                     if (u % RP == 0) {
 #pragma unroll
                         for (int c = 0; c < CH; ++c) {
-                            hi[c] = schain_window(st.ch[c], ring0 + c * THREADS * kRingBytes, acc[c] & 0xFFFFu);
+                            hi[c] = schain_window<WMASK>(st.ch[c], ring_of(c), acc[c] & 0xFFFFu);
                             acc[c] = 0;
                         }
                     }
@@ -634,7 +655,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                     bool mine = true;   // the ragged last step holds an element for the first sub-streams only
                     if constexpr (SPLIT && CHECKED) mine = (jb * kSS + u < it.nfull) || (tid * CH < it.last_active);
                     if (mine) store_syms<CH>(dst, e);
-                    if ((CHK <= kSS) ? ((u + 1) % CHK == 0) : (u == kSS - 1 && (jb & 1u))) {
+                    if (!FLAT && ((CHK <= kSS) ? ((u + 1) % CHK == 0) : (u == kSS - 1 && (jb & 1u)))) {
                         // the position used for the request is the one of the last window; the bits consumed
                         // since then (< 32) can only make the request one period late, which NEED allows for
 #pragma unroll
@@ -649,7 +670,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
         if (count == (uint32_t)kSS && !(SPLIT && it.last_active != 0u && jb + 1 == nblocks)) run_block(std::false_type{});
         else run_block(std::true_type{});
     }
-    cp_async_wait<0>();
+    if constexpr (!FLAT) cp_async_wait<0>();
     return true;
 }
 
@@ -1094,6 +1115,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
 
             // ---- streaming path: start the asynchronous copies before the tables are staged ------------
             StreamItem it;
+            it.flat_bytes = 0;
             StreamThread<L, THREADS, CH> st;
             bool stream = false;
             // rows that hold whole steps, or rows at least one step long whose length keeps 16-byte alignment
@@ -1116,6 +1138,10 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                     const uint32_t rem = (uint32_t)(total - (long long)it.nfull * k_eff);  // sub-streams with one more element
                     it.last_active = rem > t_begin ? (rem - t_begin < SPAN ? rem - t_begin : SPAN) : 0u;
                     it.nsteps = it.nfull + (it.last_active ? 1u : 0u);
+                    // a bucket whose code bits fit the space of the rings comes in with one bulk copy
+                    const long long need = (((bits + 7) >> 3) + 15) & ~15LL;   // bytes from the origin, whole 16-byte chunks
+                    if (!split && k_eff == SPAN && need <= (long long)kFlatBytes && need <= (long long)it.bo.last_ofs + 16)
+                        it.flat_bytes = (uint32_t)need;
                 }
             }
             bool run_ok = true;
@@ -1125,19 +1151,24 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             constexpr bool kInplaceFits = (kTableEntries / 8) % (2 * THREADS) == 0 && (kTableEntries / 8) / (2 * THREADS) <= 8;
             const bool tab_bulk = kInplaceFits && P.restage && P.tab_dense &&
                                   ((reinterpret_cast<uintptr_t>(T.decode_syms) | reinterpret_cast<uintptr_t>(T.decode_lens)) & 15u) == 0;
+            const bool flat = stream && it.flat_bytes != 0u;
+            const bool bulk_any = tab_bulk || flat;   // one barrier phase covers the raw tables and the resident bitstream
             const uint32_t tab_parity = tab_copies & 1u;
-            tab_inflight = tab_bulk;
+            tab_inflight = bulk_any;
             if (is_producer) {
-                if (tab_bulk && tid == THREADS) {
+                if (bulk_any && tid == THREADS) {
                     constexpr uint32_t TS = 1u << L;
-                    const uint32_t count = P.tab_count;
+                    const uint32_t count = tab_bulk ? P.tab_count : 0u;
                     const uint32_t end = smem_u32(sm.tbl) + (uint32_t)kTableEntries * 4u;
                     const uint32_t bar = smem_u32(&sm.tab_bar);
-                    // the table's space was written by ordinary stores while the previous bucket was staged
+                    // the spaces copied into were written by ordinary stores and cp.async while the previous bucket was handled
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    mbar_expect_tx(bar, (TS * 2u + TS / 2u) * count);
-                    bulk_g2s(end - (TS * 2u + TS / 2u) * count, T.decode_syms + (long long)P.tab_first * TS, TS * 2u * count, bar);
-                    bulk_g2s(end - (TS / 2u) * count, T.decode_lens + (long long)P.tab_first * (TS / 2), (TS / 2u) * count, bar);
+                    mbar_expect_tx(bar, (TS * 2u + TS / 2u) * count + (flat ? it.flat_bytes : 0u));
+                    if (tab_bulk) {
+                        bulk_g2s(end - (TS * 2u + TS / 2u) * count, T.decode_syms + (long long)P.tab_first * TS, TS * 2u * count, bar);
+                        bulk_g2s(end - (TS / 2u) * count, T.decode_lens + (long long)P.tab_first * (TS / 2), (TS / 2u) * count, bar);
+                    }
+                    if (flat) bulk_g2s(smem_u32(sm.bitring), it.bo.base, it.flat_bytes, bar);
                 }
                 if (stream) {
                     if (!split && it.k_eff == SPAN && (it.col_len & 15u) == 0u) run_ok = producer_rows<SPAN>(sm, it, blk, nblocks, stall_block, spin_limit);
@@ -1180,11 +1211,14 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                     // the raw tables never landed: the wait gave up, the CTA reports and stops below
                 } else if (stream) {
                     if (split)
-                        run_ok = staged_esc ? stream_run<L, THREADS, CH, true, true>(sm, it, st, blk, spin_limit)
-                                            : stream_run<L, THREADS, CH, false, true>(sm, it, st, blk, spin_limit);
+                        run_ok = staged_esc ? stream_run<L, THREADS, CH, true, true>(sm, it, st, blk, tab_parity, spin_limit)
+                                            : stream_run<L, THREADS, CH, false, true>(sm, it, st, blk, tab_parity, spin_limit);
+                    else if (flat)
+                        run_ok = staged_esc ? stream_run<L, THREADS, CH, true, false, true>(sm, it, st, blk, tab_parity, spin_limit)
+                                            : stream_run<L, THREADS, CH, false, false, true>(sm, it, st, blk, tab_parity, spin_limit);
                     else
-                        run_ok = staged_esc ? stream_run<L, THREADS, CH, true, false>(sm, it, st, blk, spin_limit)
-                                            : stream_run<L, THREADS, CH, false, false>(sm, it, st, blk, spin_limit);
+                        run_ok = staged_esc ? stream_run<L, THREADS, CH, true, false>(sm, it, st, blk, tab_parity, spin_limit)
+                                            : stream_run<L, THREADS, CH, false, false>(sm, it, st, blk, tab_parity, spin_limit);
                 } else if (vec) {
                     if (t0 < k_eff) {
                         if (staged_esc)
@@ -1202,7 +1236,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             }
             if (!run_ok) sm.abort = 1;
             blk += nblocks;
-            tab_copies += tab_bulk ? 1u : 0u;
+            tab_copies += bulk_any ? 1u : 0u;
         }
         if (!P.ok && tid < 32) asm volatile("bar.arrive 2, 64;" ::: "memory");
         __syncthreads();  // item done: tables, rings and the other prepared slot may now be overwritten
