@@ -286,6 +286,10 @@ def run_reference(args, rank, world):
                           "e2e": {"value": enc["processes"]["value"], "unit": "M elements/s", "h2d_bytes_per_step": 0,
                                   "d2h_bytes_per_step": 0}, "gpu_launches": 0}), flush=True)
         return
+    if args.workload == "layer":
+        print(json.dumps({"impl": "reference", "unavailable": "the layer workload times GEMMs on the GPU; the reference's CPU side "
+                                                               "has no counterpart (its call sequence is leg (a) of our arm)"}), flush=True)
+        return
     if args.workload != "model":
         return run_reference_cases(args, cores)
     cfg, tp, wname, layers = workload_for(args.gpus, args.layers)
@@ -890,6 +894,74 @@ def run_build(args, local_rank):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------
+# one decoder layer as a serving plugin uses it: decode the weights, multiply
+# ------------------------------------------------------------------------------------------------
+
+def run_layer(args, local_rank):
+    """One 8B-shaped decoder layer, weights decoded for every forward and fed to the layer's four GEMMs (16 tokens).
+    (a) the reference plugin's call sequence (scripts/mpserve_vllm_fp8_huffman.py:419, 474-489, 526-543, 657-661): one
+    ``huffman_decode_fp8`` per shard into a fresh tensor, ``torch.cat`` of q/k/v and of gate/up, ``torch.matmul``;
+    (b) the same through ``mpserve_b200.sidecar.FusedDecoder``: one launch into persistent fused weights, no cat."""
+    import MPServe_cuda
+    from mpserve_b200 import _lib
+    from mpserve_b200.sidecar import FusedDecoder
+
+    _lib.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    cfg = wl.LLAMA3_8B
+    layer = {name: (n, m, c, art) for name, n, m, c, art in encode_layer_gpu(cfg, 1, 0, args.seed, 0, dev)}
+    tokens = 16
+    x_h = torch.randn(tokens, cfg["hidden"], device=dev, dtype=torch.bfloat16)
+    x_q = torch.randn(tokens, cfg["q_heads"] * cfg["head_dim"], device=dev, dtype=torch.bfloat16)
+    x_i = torch.randn(tokens, cfg["inter"], device=dev, dtype=torch.bfloat16)
+    fused = [["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"], ["self_attn.o_proj"],
+             ["mlp.gate_proj", "mlp.up_proj"], ["mlp.down_proj"]]
+    acts = [x_h, x_q, x_h, x_i]
+
+    def one(name):
+        n, m, c, art = layer[name]
+        return MPServe_cuda.huffman_decode_fp8(c.fp8_u8, *[art[k] for k in DECODE_KEYS], n, m, 7)
+
+    def plugin_step():
+        outs = []
+        for names, x in zip(fused, acts):
+            parts = [one(nm) for nm in names]
+            w = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
+            outs.append(torch.matmul(x, w.t()))
+        return outs
+
+    dec = FusedDecoder([[(layer[nm][2].fp8_u8, {k: layer[nm][3][k] for k in DECODE_KEYS}) for nm in names] for names in fused])
+
+    def fused_step():
+        ws = dec.decode()
+        return [torch.matmul(x, w.t()) for x, w in zip(acts, ws)]
+
+    a, b = plugin_step(), fused_step()
+    torch.cuda.synchronize()
+    for u, v in zip(a, b):
+        assert torch.equal(u, v), "the fused layer's outputs differ from the plugin sequence's"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    reps = max(10, args.steps)
+    res = {}
+    for label, fn in (("plugin_sequence", plugin_step), ("fused_decoder", fused_step)):
+        med, best = _time_calls(fn, flush, reps)
+        res[label] = {"ms_median": med, "ms_best": best, "host_us": _host_us(fn, 20)}
+    clocks = sampler.stop()
+    elems = sum(n * m for n, m, _, _ in layer.values())
+    med = res["fused_decoder"]["ms_median"]
+    print(json.dumps({
+        "metric": METRIC, "value": 2 * elems / med / 1e6, "unit": UNIT, "n_gpus": 1, "steps": reps, "warmup": 3,
+        "ms_per_step": med, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16",
+        "data": "synthetic",
+        "config": {"workload": f"one llama3-8b-shaped decoder layer: decode 7 weights ({elems / 1e6:.0f} M elements) + 4 GEMMs of "
+                               f"{tokens} tokens, per forward", "l2": "a 256 MB buffer is written before every timed forward"},
+        "layer": res, "gpu_launches": None, "clocks": clocks}), flush=True)
+
+
 def run_reference_cases(args, cores):
     """CPU port on the first case of the workload (FP8 workloads), a bounded number of repetitions per step."""
     from oracle import oracle as orc
@@ -955,7 +1027,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="model", choices=["model", "single", "sizes", "awq", "build"])
+    ap.add_argument("--workload", default="model", choices=["model", "single", "sizes", "awq", "build", "layer"])
     ap.add_argument("--layers", type=int, default=None, help="shorten the model to this many layers (quicker)")
     ap.add_argument("--k", type=int, default=None, help="sub-streams per bucket for the single-tensor workloads")
     ap.add_argument("--max-bytes", type=int, default=1 << 30, help="largest BF16 output of --workload sizes")
@@ -974,6 +1046,10 @@ def main():
     if args.workload == "build":
         if rank == 0:
             run_build(args, local_rank)
+        return
+    if args.workload == "layer":
+        if rank == 0:
+            run_layer(args, local_rank)
         return
     if args.workload != "model":
         if rank == 0:
