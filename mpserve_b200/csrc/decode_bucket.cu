@@ -1380,12 +1380,14 @@ static int env_int(const char* name, int dflt) {
 
 // threads x chains = sub-streams per work item.  Wide items (more chains per thread) cost fewer
 // instructions per symbol and keep an SM 2.6 times busier than one chain per thread does; narrow
-// items give more SMs something to do when a launch has few sub-streams in total.  Halving the width
-// pays only while the wider shape would leave more than half of the SMs idle.
+// items give more SMs something to do when a launch has few sub-streams in total, and cut the largest
+// bucket, which bounds a lone tensor's time, in two.  Halving the width pays while the wider shape has
+// no more items than the GPU has SMs (measured on single tensors of 82 to 322 buckets: 129 buckets
+// decode 9 % faster halved, 188 buckets 36 % slower).
 static void pick_config(long long total_substreams, int k_min, int* threads, int* chains) {
     const int sms = sm_count();
     int t = 256, c = 4;
-    while (c > 1 && (t * c > k_min || 2 * (total_substreams / ((long long)t * c)) <= sms)) c >>= 1;
+    while (c > 1 && (t * c > k_min || total_substreams / ((long long)t * c) <= sms)) c >>= 1;
     while (t > 256 && t * c > k_min) t >>= 1;
     const int et = env_int("MPS_DECODE_THREADS", 0), ec = env_int("MPS_DECODE_CHAINS", 0);
     if (et > 0) t = et;
