@@ -198,8 +198,10 @@ MPS_API int mps_selftest_stalled_decode(const mps_bucket_tensor* tensor_host, in
  *   codebooks    fills the tables and table_scale / table_ctx [G]
  *   bucket_table fills bucket_table [B, 256|16] from the buckets' scales (bucket lists are built by
  *                the caller from the scale tensor: build_huffman.cu:611-696)
- *   rect_layout  fills bucket_thread_startbit [B,k+1] and bucket_bit_base [B+1], returns total bits
- *   rect_emit    fills bitstream_u64 [(total_bits+63)/64]
+ *   rect_layout  fills bucket_thread_startbit [B,k+1] and bucket_bit_base [B+1], returns total bits; leaves the code
+ *                of every element in the workspace for the next step
+ *   rect_emit    fills bitstream_u64 [(total_bits+63)/64]; must follow rect_layout for the same buckets, with
+ *                nothing else using the workspace in between
  * variant: 0 FP8 (context = fp8 byte), 1 AWQ-INT4 rectangular buckets (context = int4 code),
  *          3 AWQ-INT4 shared tables (analysis only; continue with the mps_build_shared_* calls below),
  *          2 AWQ-INT4 ragged buckets by exact scale (huffman_build_awq_int4_bucket_decode_tables_by_scale_entry,
