@@ -451,18 +451,31 @@ __global__ void bucket_totals_kernel(RectGeom g, unsigned long long* __restrict_
 // A CTA serves slabs of one bucket and first copies that bucket's codebooks (the symbols and codes of
 // its contexts, a few thousand items) into shared memory; a bucket with more items than fit is
 // searched in global memory instead.
-constexpr int kCodeCap = 6144;
+constexpr int kCodeCap = 6144;     // items of a bucket's codebooks that fit shared memory as (symbol, code) lists
+constexpr int kDirectCap = 9216;   // ... or, in the same space, entries of its direct maps (see below)
 constexpr int kCodeSlab = 8192;
 constexpr uint32_t kNoCode = 0xFFFFFFFFu;
+// How a CTA finds an element's code, in order of preference:
+//   direct  the symbols a context of a quantised weight sees are a few dozen neighbouring BF16 patterns, so
+//           every context gets a map indexed by (symbol - its smallest symbol); used when the maps of the
+//           bucket's contexts fit kDirectCap entries together: one shared-memory load per element;
+//   lists   the contexts' sorted symbol lists in shared memory, binary search (some hundred instructions
+//           per element, half of the lanes idle);
+//   global  the same search in global memory, for buckets whose lists do not fit either.
 __global__ void __launch_bounds__(256)
 rect_codes_kernel(RectGeom g, CodeBook cb, long long G, const unsigned long long* __restrict__ ebase, uint32_t* __restrict__ lc) {
-    __shared__ uint32_t s_ofs[257];
+    __shared__ uint32_t s_ofs[257];    // first item of every context in the lists
+    __shared__ uint32_t s_dofs[257];   // first entry of every context's direct map
+    __shared__ uint16_t s_lo[256];     // smallest symbol of every context
     __shared__ int32_t s_gid[256];
+    __shared__ int s_first[256];       // first item of every context in the global arrays
     __shared__ uint32_t s_esc[256];
     __shared__ uint16_t s_escsym[256];
-    __shared__ uint32_t s_enc[kCodeCap];
-    __shared__ uint16_t s_sym[kCodeCap];
-    __shared__ uint32_t s_warp[8];
+    __shared__ uint32_t s_pool[kDirectCap];   // direct maps, or lists: codes [kCodeCap] then symbols [kCodeCap]
+    __shared__ uint32_t s_warp[2][8];
+    static_assert(kDirectCap * 4 >= kCodeCap * 6, "the lists share the direct maps' space");
+    uint32_t* const s_enc = s_pool;
+    uint16_t* const s_sym = reinterpret_cast<uint16_t*>(s_pool + kCodeCap);
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const long long b = blockIdx.x;
     const int row_a = g.row_ofs[b];
@@ -473,43 +486,56 @@ rect_codes_kernel(RectGeom g, CodeBook cb, long long G, const unsigned long long
     const unsigned long long nslab = (total + kCodeSlab - 1) / kCodeSlab;
     if (blockIdx.y >= nslab) return;
 
-    // this bucket's contexts: table id, items, ESC code
+    // this bucket's contexts: table id, items, range of symbols, ESC code
     int32_t gid = -1;
-    uint32_t nd = 0;
+    uint32_t nd = 0, span = 0, lo_sym = 0;
+    int first = 0;
     if (tid < g.nctx) {
         gid = g.bucket_table[b * g.nctx + tid];
         if (gid >= G) gid = -1;
-        if (gid >= 0) nd = (uint32_t)(cb.ctx_ofs[gid + 1] - cb.ctx_ofs[gid]);
+        if (gid >= 0) {
+            first = cb.ctx_ofs[gid];
+            nd = (uint32_t)(cb.ctx_ofs[gid + 1] - first);
+            if (nd) {   // items are in ascending symbol order
+                lo_sym = (uint32_t)(cb.items[first] & 0xFFFF);
+                span = (uint32_t)(cb.items[first + (int)nd - 1] & 0xFFFF) - lo_sym + 1u;
+            }
+        }
     }
     s_gid[tid] = gid;
+    s_first[tid] = first;
+    s_lo[tid] = (uint16_t)lo_sym;
     s_esc[tid] = gid >= 0 ? cb.esc[gid] : 0u;
     s_escsym[tid] = gid >= 0 ? cb.escsym[gid] : (uint16_t)0;
-    uint32_t incl = nd;   // inclusive prefix of nd over the CTA
+    uint32_t incl = nd, incl_span = span;   // inclusive prefixes over the CTA
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-        if (lane >= o) incl += v;
+        const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o), vs = __shfl_up_sync(0xFFFFFFFFu, incl_span, o);
+        if (lane >= o) { incl += v; incl_span += vs; }
     }
-    if (lane == 31) s_warp[w] = incl;
+    if (lane == 31) { s_warp[0][w] = incl; s_warp[1][w] = incl_span; }
     __syncthreads();
-    uint32_t before = 0, items_total = 0;
+    uint32_t before = 0, items_total = 0, before_span = 0, span_total = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        if (i < w) before += s_warp[i];
-        items_total += s_warp[i];
+        if (i < w) { before += s_warp[0][i]; before_span += s_warp[1][i]; }
+        items_total += s_warp[0][i];
+        span_total += s_warp[1][i];
     }
     s_ofs[tid] = before + incl - nd;
-    if (tid == 255) s_ofs[256] = items_total;
+    s_dofs[tid] = before_span + incl_span - span;
+    if (tid == 255) { s_ofs[256] = items_total; s_dofs[256] = span_total; }
+    const bool direct = span_total <= (uint32_t)kDirectCap;
+    const bool staged = !direct && items_total <= (uint32_t)kCodeCap;
+    if (direct)
+        for (uint32_t i = tid; i < span_total; i += 256) s_pool[i] = kNoCode;
     __syncthreads();
-    const bool staged = items_total <= (uint32_t)kCodeCap;
-    if (staged) {
-        // first item of every context, then four copies in flight per thread
-        __shared__ int s_first[256];
-        s_first[tid] = gid >= 0 ? cb.ctx_ofs[gid] : 0;
-        __syncthreads();
+    if (direct || staged) {
+        // every item of the bucket's contexts, four copies in flight per thread
         constexpr int SUN = 4;
         for (uint32_t j0 = tid; j0 < items_total; j0 += 256 * SUN) {
             long long src[SUN];
+            int cx[SUN];
 #pragma unroll
             for (int u = 0; u < SUN; ++u) {
                 const uint32_t j = j0 + 256u * u;
@@ -518,6 +544,7 @@ rect_codes_kernel(RectGeom g, CodeBook cb, long long G, const unsigned long long
                     const int mid = (lo + hi) >> 1;
                     if (s_ofs[mid] <= j) lo = mid; else hi = mid;
                 }
+                cx[u] = lo;
                 src[u] = (j < items_total) ? (long long)s_first[lo] + (j - s_ofs[lo]) : -1;
             }
             unsigned long long it[SUN];
@@ -528,30 +555,40 @@ rect_codes_kernel(RectGeom g, CodeBook cb, long long G, const unsigned long long
                 en[u] = src[u] >= 0 ? cb.enc[src[u]] : 0u;
             }
 #pragma unroll
-            for (int u = 0; u < SUN; ++u)
-                if (src[u] >= 0) { s_sym[j0 + 256u * u] = (uint16_t)(it[u] & 0xFFFF); s_enc[j0 + 256u * u] = en[u]; }
+            for (int u = 0; u < SUN; ++u) {
+                if (src[u] < 0) continue;
+                const uint32_t sy = (uint32_t)(it[u] & 0xFFFF);
+                if (direct) s_pool[s_dofs[cx[u]] + sy - s_lo[cx[u]]] = en[u];
+                else { s_sym[j0 + 256u * u] = (uint16_t)sy; s_enc[j0 + 256u * u] = en[u]; }
+            }
         }
     }
     __syncthreads();
 
     // the code of one element
+    auto finish = [&](uint32_t lcv, uint32_t c, uint32_t sym) -> uint32_t {
+        bool raw = false;
+        if (lcv == 0) {                   // not in the codebook: the ESC code, then the raw 16 bits ...
+            lcv = s_esc[c];
+            raw = (sym != s_escsym[c]);   // ... unless the symbol is the synthetic ESC symbol itself
+        }
+        return lcv != 0 ? (lcv | (raw ? 0x80000000u : 0u)) : kNoCode;
+    };
     auto lookup = [&](uint32_t c, uint32_t sym) -> uint32_t {
         const int32_t gd = s_gid[c];
         if (gd < 0) return kNoCode;
+        if (direct) {
+            const uint32_t d = sym - s_lo[c], at = s_dofs[c];
+            if (d >= s_dofs[c + 1] - at) return kNoCode;
+            const uint32_t lcv = s_pool[at + d];
+            return lcv == kNoCode ? kNoCode : finish(lcv, c, sym);
+        }
         if (staged) {
             int lo = (int)s_ofs[c], hi = (int)s_ofs[c + 1] - 1;
             while (lo <= hi) {
                 const int mid = (lo + hi) >> 1;
                 const uint32_t x = s_sym[mid];
-                if (x == sym) {
-                    uint32_t lcv = s_enc[mid];
-                    bool raw = false;
-                    if (lcv == 0) {                   // not in the codebook: the ESC code, then the raw 16 bits ...
-                        lcv = s_esc[c];
-                        raw = (sym != s_escsym[c]);   // ... unless the symbol is the synthetic ESC symbol itself
-                    }
-                    return lcv != 0 ? (lcv | (raw ? 0x80000000u : 0u)) : kNoCode;
-                }
+                if (x == sym) return finish(s_enc[mid], c, sym);
                 if (x < sym) lo = mid + 1; else hi = mid - 1;
             }
             return kNoCode;
