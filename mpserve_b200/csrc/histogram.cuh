@@ -77,8 +77,9 @@ __global__ void unit_scatter_kernel(Geom g, const uint16_t* __restrict__ scales,
         unit_sorted[atomicAdd(&unit_cur[unit_scale(g, scales, u)], 1u)] = (uint32_t)u;
 }
 
-// Calls f(context, symbol) for every element of unit u, lanes striding along rows, four elements of a
-// lane loaded before any is handed on (so that four loads are in flight per lane, not one).
+// Calls f(context, symbol) for every element of unit u, lanes striding along rows, four (eight when the
+// symbols are read too) elements of a lane loaded before any is handed on, so that as many loads are in
+// flight per lane, not one.
 template <bool WITH_SYM, class F>
 __device__ __forceinline__ void for_unit_elements(const Geom& g, long long u, int lane, const uint8_t* __restrict__ ctx,
                                                   const uint16_t* __restrict__ sym, F&& f) {
@@ -86,7 +87,7 @@ __device__ __forceinline__ void for_unit_elements(const Geom& g, long long u, in
     const long long r0 = bi * g.ub0, c0 = bj * g.ub1;
     const long long r1 = (r0 + g.ub0 < g.n) ? r0 + g.ub0 : g.n;
     const long long c1 = (c0 + g.ub1 < g.m) ? c0 + g.ub1 : g.m;
-    constexpr int UN = 4;
+    constexpr int UN = WITH_SYM ? 8 : 4;
     for (long long r = r0; r < r1; ++r) {
         const uint8_t* crow = ctx + r * g.m;
         const uint16_t* srow = sym + r * g.m;
