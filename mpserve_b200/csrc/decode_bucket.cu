@@ -14,11 +14,13 @@
 //    while the current one is decoded;
 //  * per item the bucket's tables are fused once into 32-bit entries sym << 16 | esc | len laid out
 //    [ctx][prefix], so a symbol costs ONE shared-memory load; staging is skipped when the next item
-//    uses the same tables;
+//    uses the same tables; tables that are one run of table ids (what the reference encoder writes) are
+//    bulk-copied raw into the table's own space and expanded in place;
 //  * each thread decodes CH adjacent sub-streams in lock-step: CH independent dependency chains for
 //    ILP, one CH-byte context read and one 2*CH-byte BF16 store per step, both fully coalesced across
 //    the warp; context bytes arrive through cp.async.bulk issued by a producer warp, the bitstream
-//    through a ring of 16-byte cp.async chunks per sub-stream;
+//    through a ring of 16-byte cp.async chunks per sub-stream, or whole with one bulk copy when the
+//    bucket's code bits fit the rings' space;
 //  * every sub-stream decodes from a 32-bit left-aligned window that is rebuilt from its bit position
 //    every (32 - L) / L + 1 symbols, branch-free, so that the rebuild is warp-uniform;
 //  * ESC (raw 16-bit symbol after the code) is rare: buckets whose tables contain no ESC entry run
