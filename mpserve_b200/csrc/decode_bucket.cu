@@ -478,6 +478,47 @@ __device__ __forceinline__ bool producer_rows(Smem& sm, const StreamItem& it, ui
     return true;
 }
 
+// Rows shorter than a step (the groups of an AWQ sidecar are 128 elements, a step of 256 sub-streams is
+// two of them): a step is a whole number of rows, each copied as one piece; the decoding threads find
+// their own row of a step themselves (stream_run, MROW).
+template <int SPAN>
+__device__ __forceinline__ bool producer_mrow(Smem& sm, const StreamItem& it, uint32_t blk, uint32_t nblocks, int stall_block,
+                                              uint32_t spin_limit) {
+    constexpr uint32_t NST = ring_stages(SPAN);
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t rows_item = SPAN / it.col_len;        // rows of a step that hold this item's sub-streams
+    const uint32_t rows_step = it.k_eff / it.col_len;    // rows of a step of the bucket
+    const uint32_t row0 = it.t_begin / it.col_len;
+    for (uint32_t jb = 0; jb < nblocks; ++jb) {
+        const uint32_t g = blk + jb, stage = g % NST, round = g / NST;
+        const uint32_t full = smem_u32(&sm.full_bar[stage]);
+        const uint32_t left = it.nsteps - jb * kSS;
+        const uint32_t nst = left < (uint32_t)kSS ? left : (uint32_t)kSS;
+        int good = 1;
+        if (lane == 0) {
+            good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u, spin_limit) ? 1 : 0;
+            uint32_t bytes = nst * SPAN;
+            if (it.nsteps > it.nfull && jb * kSS + nst == it.nsteps) bytes -= SPAN - it.last_active;  // ragged last step: fewer rows
+            if (good) {
+                mbar_expect_tx(full, bytes);
+                sm.armed = g + 1;
+            }
+        }
+        good = __shfl_sync(0xFFFFFFFFu, good, 0);
+        if (!good) return false;
+        if (lane < (uint32_t)kSS) mbar_arrive(full);
+        if ((int)g == stall_block) continue;   // self-test: the bytes never come, the consumers' wait runs out
+        for (uint32_t p = lane; p < nst * rows_item; p += 32u) {
+            const uint32_t u = p / rows_item, j = p - u * rows_item;
+            const uint32_t row = (jb * kSS + u) * rows_step + row0 + j;
+            if (row < it.nrows)
+                bulk_g2s(smem_u32(sm.ctxring) + (stage * kSS + u) * SPAN + j * it.col_len,
+                         it.ctx_bytes + it.rowbase[row < kRowCap ? row : 0], it.col_len, full);
+        }
+    }
+    return true;
+}
+
 template <int L, int THREADS, int CH>
 struct StreamThread {  // per-thread state that lives from stream_begin to stream_run
     SChain ch[CH];
@@ -516,10 +557,17 @@ __device__ __forceinline__ void stream_begin(Smem& sm, const StreamItem& it, Str
 
 // FLAT: the bucket's bitstream was bulk-copied whole into the space of the rings (a bucket of up to 64 KB of
 // code bits: the attention projections, every shard of them): no first chunks to fetch, no requests in the loop.
-template <int L, int THREADS, int CH, bool ESC, bool SPLIT, bool FLAT = false>
+// MROW: rows shorter than a step; a thread's element of step s lies in row s * (rows per step) + (its own row of
+// the step), whose start it reads from the row bases in shared memory (see producer_mrow).
+template <int L, int THREADS, int CH, bool ESC, bool SPLIT, bool FLAT = false, bool MROW = false>
 __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, StreamThread<L, THREADS, CH>& st,
                                            uint32_t blk, uint32_t bulk_parity, uint32_t spin_limit) {
-    static_assert(!(FLAT && SPLIT), "the resident-bitstream loop serves rows that hold whole steps");
+    static_assert(!(FLAT && SPLIT) && !(MROW && (SPLIT || FLAT)), "one special shape at a time");
+    // (MROW) this thread's row within a step, its column in that row, rows per step of the bucket
+    const uint32_t my_row = MROW ? (it.t_begin + threadIdx.x * CH) / it.col_len : 0u;
+    const uint32_t my_col = MROW ? (it.t_begin + threadIdx.x * CH) - my_row * it.col_len : 0u;
+    const uint32_t rows_step = MROW ? it.k_eff / it.col_len : 0u;
+    const uint32_t rowbase_s = MROW ? smem_u32(it.rowbase) : 0u;
     constexpr uint32_t WMASK = FLAT ? kFlatMask : 60u;
     constexpr int RP = ESC ? 1 : ((32 - L) / L + 1);   // symbols per 32-bit window
     // Steps between bitstream requests: rare requests cost fewer instructions, frequent ones let
@@ -652,10 +700,15 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                     }
                     uint32_t o = ofs[u];
                     if constexpr (SPLIT) o = (tid * CH >= split[u]) ? ofs_b[u] : o;
+                    if constexpr (MROW) {
+                        const uint32_t row = (jb * kSS + (uint32_t)u) * rows_step + my_row;
+                        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(o) : "r"(rowbase_s + 4u * (row < (uint32_t)kRowCap ? row : 0u)) : "memory");
+                        o += my_col;   // the element's own offset: added to the tensor's start below, not to out0
+                    }
                     uint16_t* dst;   // out0 + o elements, as one multiply-add
-                    asm("mad.wide.u32 %0, %1, 2, %2;" : "=l"(dst) : "r"(o), "l"(out0));
+                    asm("mad.wide.u32 %0, %1, 2, %2;" : "=l"(dst) : "r"(o), "l"(MROW ? it.out : out0));
                     bool mine = true;   // the ragged last step holds an element for the first sub-streams only
-                    if constexpr (SPLIT && CHECKED) mine = (jb * kSS + u < it.nfull) || (tid * CH < it.last_active);
+                    if constexpr ((SPLIT || MROW) && CHECKED) mine = (jb * kSS + u < it.nfull) || (tid * CH < it.last_active);
                     if (mine) store_syms<CH>(dst, e);
                     if (!FLAT && ((CHK <= kSS) ? ((u + 1) % CHK == 0) : (u == kSS - 1 && (jb & 1u)))) {
                         // the position used for the request is the one of the last window; the bits consumed
@@ -669,7 +722,7 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
             }
         };
         // (the block that holds a ragged last step always takes the checked form)
-        if (count == (uint32_t)kSS && !(SPLIT && it.last_active != 0u && jb + 1 == nblocks)) run_block(std::false_type{});
+        if (count == (uint32_t)kSS && !((SPLIT || MROW) && it.last_active != 0u && jb + 1 == nblocks)) run_block(std::false_type{});
         else run_block(std::true_type{});
     }
     if constexpr (!FLAT) cp_async_wait<0>();
@@ -1122,8 +1175,14 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
             bool stream = false;
             // rows that hold whole steps, or rows at least one step long whose length keeps 16-byte alignment
             const bool split = (col_len % k_eff) != 0;
+            // rows shorter than a step: a step is whole rows, and so is this item's share of it
+            // (instantiated for one or two chains per thread only: such buckets have few sub-streams, and the widest
+            // kernel, which decodes whole models, is at its register limit)
+            constexpr bool kMrowBuilt = CH <= 2;
+            const bool mrow = kMrowBuilt && col_len < k_eff && (k_eff % col_len) == 0 && (SPAN % col_len) == 0 &&
+                              (t_begin % col_len) == 0 && (col_len % 16) == 0 && total < 0xFFFFFFFFLL;
             if (vec && P.rows_al16 && t_begin + SPAN <= k_eff && (k_eff % 16u) == 0 &&
-                (!split || (col_len > k_eff && (col_len % 16) == 0 && total < 0xFFFFFFFFLL)) &&
+                (!split || mrow || (col_len > k_eff && (col_len % 16) == 0 && total < 0xFFFFFFFFLL)) &&
                 ((reinterpret_cast<uintptr_t>(T.ctx_bytes) & 15u) == 0)) {
                 const uint8_t* bucket_bytes = reinterpret_cast<const uint8_t*>(T.bitstream) + 8 * wb;
                 const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(bucket_bytes) & 15u);  // 0 or 8
@@ -1135,7 +1194,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                     it.ctx_bytes = T.ctx_bytes; it.out = T.out; it.startbit = startbit; it.rowbase = rowbase;
                     it.bo.base = bucket_bytes - mis; it.bo.last_ofs = (uint32_t)((valid - 16) & ~15LL); it.bo.bit_delta = 8 * mis + P.bit_lo;
                     it.bo.tail_ofs = (valid & 8) ? it.bo.last_ofs + 16u : 0xFFFFFFFFu;
-                    it.t_begin = t_begin; it.k_eff = k_eff; it.col_len = (uint32_t)col_len;
+                    it.t_begin = t_begin; it.k_eff = k_eff; it.col_len = (uint32_t)col_len; it.nrows = (uint32_t)nrows;
                     it.nfull = (uint32_t)(total / k_eff);
                     const uint32_t rem = (uint32_t)(total - (long long)it.nfull * k_eff);  // sub-streams with one more element
                     it.last_active = rem > t_begin ? (rem - t_begin < SPAN ? rem - t_begin : SPAN) : 0u;
@@ -1173,7 +1232,12 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                     if (flat) bulk_g2s(smem_u32(sm.bitring), it.bo.base, it.flat_bytes, bar);
                 }
                 if (stream) {
-                    if (!split && it.k_eff == SPAN && (it.col_len & 15u) == 0u) run_ok = producer_rows<SPAN>(sm, it, blk, nblocks, stall_block, spin_limit);
+                    bool fed = false;
+                    if constexpr (kMrowBuilt) {
+                        if (mrow) { run_ok = producer_mrow<SPAN>(sm, it, blk, nblocks, stall_block, spin_limit); fed = true; }
+                    }
+                    if (fed) {
+                    } else if (!split && it.k_eff == SPAN && (it.col_len & 15u) == 0u) run_ok = producer_rows<SPAN>(sm, it, blk, nblocks, stall_block, spin_limit);
                     else run_ok = split ? producer_run<SPAN, true>(sm, it, blk, nblocks, stall_block, spin_limit)
                                         : producer_run<SPAN, false>(sm, it, blk, nblocks, stall_block, spin_limit);
                 }
@@ -1212,7 +1276,16 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                 if (!run_ok) {
                     // the raw tables never landed: the wait gave up, the CTA reports and stops below
                 } else if (stream) {
-                    if (split)
+                    bool ran = false;
+                    if constexpr (kMrowBuilt) {
+                        if (mrow) {
+                            run_ok = staged_esc ? stream_run<L, THREADS, CH, true, false, false, true>(sm, it, st, blk, tab_parity, spin_limit)
+                                                : stream_run<L, THREADS, CH, false, false, false, true>(sm, it, st, blk, tab_parity, spin_limit);
+                            ran = true;
+                        }
+                    }
+                    if (ran) {
+                    } else if (split)
                         run_ok = staged_esc ? stream_run<L, THREADS, CH, true, true>(sm, it, st, blk, tab_parity, spin_limit)
                                             : stream_run<L, THREADS, CH, false, true>(sm, it, st, blk, tab_parity, spin_limit);
                     else if (flat)

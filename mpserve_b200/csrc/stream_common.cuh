@@ -57,6 +57,7 @@ struct StreamItem {
     uint32_t nfull;        // steps in which every sub-stream of the bucket has an element
     uint32_t last_active;  // local sub-streams that have an element in the ragged last step (0: there is none)
     uint32_t flat_bytes;   // != 0: the bucket's whole bitstream, this many bytes from bo.base, is copied into shared memory
+    uint32_t nrows;        // rows (groups) of the bucket
 };
 
 constexpr uint32_t kSpinLimit = 1u << 22;  // bounded waits: give up, flag, return
