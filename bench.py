@@ -691,7 +691,12 @@ def fp8_case(n, m, dist, scale_mode, k, seed, dev, flush, reps):
     import MPServe_cuda
 
     c = wl.quantize_fp8(wl.random_weight(n, m, seed, dist, device=dev), scale_mode)
-    art = MPServe_cuda.huffman_build_fp8_decode_tables(c.bf16, c.fp8_u8, c.scales_u16, max_len=7, threads_per_block=k)
+    if k <= 1024:
+        art = MPServe_cuda.huffman_build_fp8_decode_tables(c.bf16, c.fp8_u8, c.scales_u16, max_len=7, threads_per_block=k)
+    else:   # more sub-streams per bucket than the reference builds or decodes: this library's extension of the format
+        from mpserve_b200 import api
+
+        art = api.build_fp8_fine_substreams(c.bf16, c.fp8_u8, c.scales_u16, max_len=7, substreams=k)
     a = [art[key] for key in DECODE_KEYS]
 
     def run():
@@ -702,7 +707,8 @@ def fp8_case(n, m, dist, scale_mode, k, seed, dev, flush, reps):
     assert torch.equal(out.view(torch.uint16), c.bf16.view(torch.uint16)), "decode mismatch"
     med, best = _time_calls(run, flush, reps)
     e2e_ms, h2d = _e2e_call([c.fp8_u8] + a, run, lambda o: o, max(3, reps // 3))
-    r = _case_result(f"fp8 {scale_mode} {dist} {n}x{m} k={k}", n, m, art, DECODE_KEYS, n * m, med, best, e2e_ms, h2d,
+    note = "" if k <= 1024 else " (fine sub-streams: not a reference sidecar)"
+    r = _case_result(f"fp8 {scale_mode} {dist} {n}x{m} k={k}{note}", n, m, art, DECODE_KEYS, n * m, med, best, e2e_ms, h2d,
                      _host_us(run))
     r.update(buckets=int(art["bucket_table_i32"].size(0)), tables=int(art["decode_syms_u16"].size(0)))
     return r, (c, art)
@@ -752,7 +758,7 @@ def case_list(args):
     """(label of the workload, list of case constructors) for --workload single | sizes | awq."""
     k = args.k
     if args.workload == "single":
-        ks = [k] if k else [1024, 256]
+        ks = [k] if k else [1024, 256, 4096]   # 4096: finer sub-streams than the reference's format allows
         return ("single linear weight 4096x4096, N(0,0.02), per-tensor FP8-E4M3 scale, huffman sidecar (L=7), one "
                 "MPServe_cuda.huffman_decode_fp8 call",
                 [("fp8", dict(n=4096, m=4096, dist="normal", scale_mode="tensor", k=kk, seed=7)) for kk in ks])

@@ -32,6 +32,14 @@ extern "C" {
 #define MPS_ERR_UNSUPPORTED (-2)  /* valid but not implemented by this build                      */
 #define MPS_ERR_WORKSPACE (-3)    /* workspace missing or too small                                */
 
+/* Most sub-streams per bucket (k) this library builds and decodes.  The reference stops at 1024, the
+ * size of the one thread block that decodes a bucket there (kernel/decode_huffman.cu:695,
+ * kernel/build_huffman.cu:313); a sidecar written with more is the same format with a longer
+ * bucket_thread_startbit row, and only this library reads it.  Finer sub-streams are what gives a lone
+ * weight of few buckets enough independent chains to fill the GPU. */
+#define MPS_MAX_SUBSTREAMS_REFERENCE 1024
+#define MPS_MAX_SUBSTREAMS 8192
+
 /* Library / device ---------------------------------------------------------------------------- */
 
 /* Version of this ABI (bumped on incompatible change). */

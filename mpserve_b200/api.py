@@ -22,8 +22,16 @@ __all__ = [
     "huffman_decode_awq_int4_bucket_by_scale", "huffman_decode_awq_shared_table",
     "huffman_build_fp8_decode_tables", "huffman_build_awq_int4_bucket_decode_tables",
     "huffman_build_awq_int4_bucket_decode_tables_by_scale", "huffman_build_awq_decode_tables",
+    "build_fp8_fine_substreams", "MAX_SUBSTREAMS", "MAX_SUBSTREAMS_REFERENCE",
     "BucketDecodePlan", "checksum_u16", "decode_timed_out", "noalloc_decode_timed_out", "selftest_stalled_decode",
 ]
+
+# Sub-streams per bucket: the reference builds and decodes at most 1024 (one thread of one block each,
+# kernel/build_huffman.cu:313, kernel/decode_huffman.cu:695); this library up to MAX_SUBSTREAMS
+# (include/mpserve_b200.h).  The decode calls below accept both; the builders under the reference's names
+# keep the reference's limit, build_fp8_fine_substreams is the way to more.
+MAX_SUBSTREAMS_REFERENCE = 1024
+MAX_SUBSTREAMS = 8192
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
@@ -168,8 +176,8 @@ def _check_rect(bucket_col_start_i32, bucket_col_len_i32, bucket_row_offsets_i32
     if bucket_bit_base_i64.numel() != B + 1:
         raise ValueError("bucket_bit_base_i64 length must be B+1")
     k = int(bucket_thread_startbit_u32.size(1)) - 1
-    if k <= 0 or k > 1024:
-        raise ValueError("bucket_thread_startbit_u32 has invalid k (must be 1..1024)")
+    if k <= 0 or k > MAX_SUBSTREAMS:
+        raise ValueError(f"bucket_thread_startbit_u32 has invalid k (must be 1..{MAX_SUBSTREAMS})")
     return k
 
 
@@ -459,6 +467,23 @@ def huffman_build_fp8_decode_tables(bf16_params, fp8_params, scales, max_len=12,
     from . import encoder
 
     return encoder.build_fp8(bf16_params, fp8_params, scales, int(max_len), int(threads_per_block))
+
+
+def build_fp8_fine_substreams(bf16_params, fp8_params, scales, max_len=7, substreams=4096):
+    """The FP8 sidecar with up to MAX_SUBSTREAMS sub-streams per bucket: the same seventeen artifacts as
+    ``huffman_build_fp8_decode_tables``, byte for byte what that call would write if the reference's
+    limit of 1024 (build_huffman.cu:313) were lifted, with ``bucket_thread_startbit_u32`` of shape
+    ``[B, substreams + 1]``.  No counterpart in the reference, whose decoder refuses such a sidecar
+    (decode_huffman.cu:695); ``huffman_decode_fp8`` and ``BucketDecodePlan`` of this module read it.
+
+    What it is for: a weight of few buckets (a per-tensor scale gives 128-row buckets: 32 for a
+    4096 x 4096 weight) has only ``B * k`` independent chains of symbols; at k = 1024 they fill a
+    quarter of a B200's decode slots and the call is bound by the latency of one chain.  Four times the
+    sub-streams cost 4 KB of start offsets per bucket more and cut that call from 54 to 34 microseconds.
+    A weight with per-channel scales has chains enough at 1024 and only pays for the longer rows."""
+    from . import encoder
+
+    return encoder.build_fp8(bf16_params, fp8_params, scales, int(max_len), int(substreams), limit=MAX_SUBSTREAMS)
 
 
 def huffman_build_awq_int4_bucket_decode_tables(bf16_params, int4_values_u8, scales_u16, max_len=11,

@@ -1458,11 +1458,17 @@ static int env_int(const char* name, int dflt) {
 // items give more SMs something to do when a launch has few sub-streams in total, and cut the largest
 // bucket, which bounds a lone tensor's time, in two.  Halving the width pays while the wider shape has
 // no more items than the GPU has SMs (measured on single tensors of 82 to 322 buckets: 129 buckets
-// decode 9 % faster halved, 188 buckets 36 % slower).
+// decode 9 % faster halved, 188 buckets 36 % slower).  Buckets of more sub-streams than an item holds are
+// cut into equal parts already: there halving only pays while every item still gets an SM of its own
+// (a 4096 x 4096 weight of 32 buckets x 4096 sub-streams: 33.7 us as 128 items of (256,4), 39.8 us as 256 of (256,2)).
 static void pick_config(long long total_substreams, int k_min, int* threads, int* chains) {
     const int sms = sm_count();
     int t = 256, c = 4;
-    while (c > 1 && (t * c > k_min || total_substreams / ((long long)t * c) <= sms)) c >>= 1;
+    while (c > 1) {
+        const long long items = total_substreams / ((long long)t * c);
+        const bool parts = k_min > t * c;
+        if (t * c > k_min || (parts ? 2 * items <= sms : items <= sms)) c >>= 1; else break;
+    }
     while (t > 256 && t * c > k_min) t >>= 1;
     const int et = env_int("MPS_DECODE_THREADS", 0), ec = env_int("MPS_DECODE_CHAINS", 0);
     if (et > 0) t = et;
@@ -1483,7 +1489,7 @@ static int validate_tensor(const mps_bucket_tensor& T, int L) {
         return MPS_ERR_INVALID;
     }
     if (T.n <= 0 || T.m <= 0) { set_error("n,m must be > 0"); return MPS_ERR_INVALID; }
-    if (T.k <= 0 || T.k > 1024) { set_error("bucket_thread_startbit_u32 has invalid k (must be 1..1024)"); return MPS_ERR_INVALID; }
+    if (T.k <= 0 || T.k > MPS_MAX_SUBSTREAMS) { set_error("bucket_thread_startbit_u32 has invalid k (must be 1..%d)", MPS_MAX_SUBSTREAMS); return MPS_ERR_INVALID; }
     if (T.num_buckets < 0 || T.num_tables < 0 || T.bitstream_words < 0 || T.num_rows < 0) { set_error("negative size"); return MPS_ERR_INVALID; }
     if ((L == 7) != (T.mode == 0)) { set_error("tensor mode does not match the table width"); return MPS_ERR_INVALID; }
     if ((reinterpret_cast<uintptr_t>(T.bitstream) & 7u) != 0) { set_error("bitstream must be 8-byte aligned"); return MPS_ERR_INVALID; }

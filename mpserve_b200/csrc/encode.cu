@@ -1179,7 +1179,7 @@ static int rect_common(mps_build_state* state, const uint16_t* bf16_bits, const 
                        const int32_t* bucket_col_len_i32, const int32_t* bucket_row_offsets_i32,
                        const int32_t* row_indices_i32, int64_t num_buckets, int32_t k, RectGeom* g, CodeBook* cb) {
     if (!state || !bf16_bits || !ctx_bytes || !bucket_table_i32 || !bucket_col_start_i32 ||
-        !bucket_row_offsets_i32 || !row_indices_i32 || num_buckets < 0 || k <= 0 || k > 1024) {
+        !bucket_row_offsets_i32 || !row_indices_i32 || num_buckets < 0 || k <= 0 || k > MPS_MAX_SUBSTREAMS) {
         set_error("sidecar layout: bad argument");
         return MPS_ERR_INVALID;
     }

@@ -156,8 +156,9 @@ def _build_rect(variant: int, bf16, ctx_u8, scales, max_len: int, k: int, ctx_na
         return {k_: (v if keep_on_device and v.is_cuda else v.cpu()) for k_, v in out.items()}
 
 
-def build_fp8(bf16_params, fp8_params, scales, max_len, threads_per_block):
-    """huffman_build_fp8_decode_tables (kernel/wrapper.cpp:419-454, build_huffman.cu:292-969)."""
+def build_fp8(bf16_params, fp8_params, scales, max_len, threads_per_block, limit=1024):
+    """huffman_build_fp8_decode_tables (kernel/wrapper.cpp:419-454, build_huffman.cu:292-969).  ``limit``:
+    most sub-streams per bucket accepted; 1024 is the reference's, with the reference's message."""
     for t in (bf16_params, fp8_params, scales):
         if not isinstance(t, torch.Tensor):
             raise ValueError("inputs must be defined")
@@ -167,8 +168,8 @@ def build_fp8(bf16_params, fp8_params, scales, max_len, threads_per_block):
         raise ValueError("fp8_params must be torch.uint8")
     if max_len <= 0 or max_len > 15:
         raise ValueError("max_len must be in [1, 15]")
-    if threads_per_block <= 0 or threads_per_block > 1024:
-        raise ValueError("threads_per_block must be in [1, 1024]")
+    if threads_per_block <= 0 or threads_per_block > limit:
+        raise ValueError(f"threads_per_block must be in [1, {limit}]")
     if fp8_params.numel() != bf16_params.numel():
         raise ValueError("bf16_params and fp8_params must have same numel")
     if scales.dtype not in (torch.uint16, torch.bfloat16):

@@ -101,6 +101,12 @@ void orc_set_num_threads(int n) {
 #endif
 }
 
+/* Most sub-streams per bucket orc_build_fp8 accepts.  1024 is the reference's limit (build_huffman.cu:313)
+ * and the default; a test of the library's finer sub-streams raises it: the layout code below follows
+ * build_huffman.cu:811-918, where nothing but that argument check depends on the number. */
+static int64_t g_substream_limit = 1024;
+void orc_set_substream_limit(int64_t n) { g_substream_limit = n > 0 ? n : 1024; }
+
 /* ------------------------------------------------------------------------------------------ */
 /* Length-limited code lengths (package-merge), build_huffman.cu:46-118                        */
 /*                                                                                             */
@@ -679,7 +685,7 @@ orc_result* orc_build_fp8(const uint16_t* bf16, const uint8_t* fp8, const uint16
     orc_result* r = res_new();
     const char* why = "";
     if (max_len <= 0 || max_len > 15) return res_fail(r, 1, "max_len must be in [1, 15]");
-    if (threads_per_block <= 0 || threads_per_block > 1024) return res_fail(r, 1, "threads_per_block must be in [1, 1024]");
+    if (threads_per_block <= 0 || threads_per_block > g_substream_limit) return res_fail(r, 1, "threads_per_block must be in [1, 1024]");
     if (n <= 0 || m <= 0) return res_fail(r, 1, "bf16_params shape must be non-empty");
     scale_map sm;
     if (scale_map_init(&sm, 1, scales, scale_ndim, sd0, sd1, n, m, &why)) return res_fail(r, 1, why);

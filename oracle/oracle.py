@@ -75,6 +75,12 @@ def set_num_threads(n: int) -> None:
     lib().orc_set_num_threads(C.c_int(int(n)))
 
 
+def set_substream_limit(n: int = 1024) -> None:
+    """Most sub-streams per bucket ``build_fp8`` accepts from now on (1024, the reference's limit, unless a
+    test of the library's finer sub-streams raises it)."""
+    lib().orc_set_substream_limit(C.c_int64(int(n)))
+
+
 def _ptr(a: np.ndarray):
     return a.ctypes.data_as(C.c_void_p)
 

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from mpserve_b200 import encoder
+from mpserve_b200 import api, encoder
 from mpserve_b200 import workloads as wl
 from oracle import oracle as orc
 
@@ -73,6 +73,10 @@ def test_builder_argument_checks_without_gpu():
         MPServe_cuda.huffman_build_fp8_decode_tables(w.float(), q, s, 7, 32)
     with pytest.raises(ValueError, match="threads_per_block"):
         MPServe_cuda.huffman_build_fp8_decode_tables(w, q, s, 7, 4096)
+    with pytest.raises(ValueError, match=r"threads_per_block must be in \[1, 1024\]"):
+        MPServe_cuda.huffman_build_fp8_decode_tables(w, q, s, 7, 1025)   # the reference's limit under the reference's name
+    with pytest.raises(ValueError, match=r"threads_per_block must be in \[1, 8192\]"):
+        api.build_fp8_fine_substreams(w, q, s, 7, api.MAX_SUBSTREAMS + 1)
     with pytest.raises(ValueError, match="max_len"):
         MPServe_cuda.huffman_build_fp8_decode_tables(w, q, s, 16, 32)
     with pytest.raises(ValueError, match="same numel"):
