@@ -953,12 +953,17 @@ __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws,
     // Work queue with guided grabs: consecutive items belong to the same tensor more often than not, so
     // a CTA that takes several in a row stages that tensor's tables once for all of them.  The grab
     // shrinks to single items towards the end of the launch, where balance matters more than reuse.
-    if (q_cur >= q_end) {
+    if (wait_iter < 0) {
+        // A CTA's first item is the one of its own number: a launch starts without a round trip to the queue
+        // counter, which therefore counts from the grid size on.
+        q_cur = (int)blockIdx.x < args.total_items ? (int)blockIdx.x : args.total_items;
+        q_end = q_cur < args.total_items ? q_cur + 1 : q_cur;
+    } else if (q_cur >= q_end) {
         const int remaining = args.total_items - q_cur;  // q_cur: end of this CTA's last grab, a lower bound of the queue head
         int want = remaining / (int)(kGrabSlack * gridDim.x);
         want = want < 1 ? 1 : (want > kMaxGrab ? kMaxGrab : want);
         unsigned int start = 0;
-        if (lane == 0) start = atomicAdd(&ws[0], (unsigned int)want);
+        if (lane == 0) start = atomicAdd(&ws[0], (unsigned int)want) + gridDim.x;
         start = __shfl_sync(0xFFFFFFFFu, start, 0);
         if (start >= (unsigned int)args.total_items) {
             q_cur = q_end = args.total_items;  // queue exhausted
@@ -1001,14 +1006,25 @@ __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws,
     const uint32_t chunks = (k + SPAN - 1) / SPAN;
     const long long b = local / chunks;
     const uint32_t chunk = (uint32_t)(local - b * chunks);
+    // Everything that depends on the bucket's number alone is requested before any of it is used: the scout's
+    // time for an item is a chain of round trips to memory, and a launch's first item has nothing to hide it behind.
     const long long row_a = T.bucket_row_offsets[b];
-    const long long nrows = (long long)T.bucket_row_offsets[b + 1] - row_a;
+    const long long row_e = T.bucket_row_offsets[b + 1];
     long long col_start = 0, col_len = T.group_size;
     if (mode != 2) { col_start = T.bucket_col_start[b]; col_len = T.bucket_col_len[b]; }
+    const long long bit_base = T.bucket_bit_base[b];
+    const uint32_t* const startbit = T.thread_startbit + b * ((long long)k + 1);
+    const uint32_t ebits_k = startbit[k];    // the bucket's bits, unless it has fewer elements than sub-streams
+    int32_t gids[(NCTX + 31) / 32];
+#pragma unroll
+    for (int j = 0; j < (NCTX + 31) / 32; ++j) {
+        const int c = lane + 32 * j;
+        gids[j] = (c < NCTX) ? T.bucket_table[b * NCTX + c] : -1;
+    }
+    const long long nrows = row_e - row_a;
     const long long total = nrows * col_len;
     bool ok = nrows > 0 && col_len > 0 && row_a >= 0 && row_a + nrows <= T.num_rows &&
               (mode == 2 || (col_start >= 0 && col_start + col_len <= T.m));
-    const long long bit_base = T.bucket_bit_base[b];
     const long long wb = bit_base >> 6;
     ok = ok && bit_base >= 0 && wb < T.bitstream_words;
     uint32_t k_eff = k;
@@ -1018,12 +1034,11 @@ __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws,
 
     int rows_ok = 1, rows_vec = 1, rows_al16 = 1;
     uint32_t ebits = 0;
-    int32_t gids[(NCTX + 31) / 32];
 #pragma unroll
-    for (int j = 0; j < (NCTX + 31) / 32; ++j) gids[j] = -1;
+    for (int j = 0; j < (NCTX + 31) / 32; ++j)
+        if (!ok || gids[j] >= T.num_tables) gids[j] = -1;
     if (ok) {
-        const uint32_t* startbit = T.thread_startbit + b * ((long long)k + 1);
-        ebits = startbit[k_eff];
+        ebits = (k_eff == k) ? ebits_k : startbit[k_eff];
         // row bases of the bucket (element offset of each row / group start)
         const long long ncache = nrows < kRowCap ? nrows : kRowCap;
         for (long long i = lane; i < ncache; i += 32) {
@@ -1040,13 +1055,6 @@ __device__ void scout_prepare(const BatchArgs& args, Smem& sm, unsigned int* ws,
         rows_vec = __all_sync(0xFFFFFFFFu, rows_vec);
         rows_al16 = __all_sync(0xFFFFFFFFu, rows_al16);
         // pull what the item will read first into L2: its tables, its sub-stream offsets
-#pragma unroll
-        for (int j = 0; j < (NCTX + 31) / 32; ++j) {
-            const int c = lane + 32 * j;
-            int32_t gid = (c < NCTX) ? T.bucket_table[b * NCTX + c] : -1;
-            if (gid >= T.num_tables) gid = -1;
-            gids[j] = gid;
-        }
 #pragma unroll
         for (int j = 0; j < (NCTX + 31) / 32; ++j) {
             const int32_t gid = gids[j];
