@@ -363,71 +363,128 @@ __device__ __forceinline__ void chunk_fetch(uint32_t ring, const BitOrigin& bo, 
     else if (ofs == bo.tail_ofs) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(bo.base + ofs) : "memory");
 }
 
-// Producer warp.  Lane 0 waits until every consumer warp has released the stage and arms its "full"
-// barrier with the bytes to come; lanes 0..kSS-1 then issue one bulk copy each (the context bytes of
-// one step), so a block of steps costs the producer one round of address arithmetic, not kSS rounds
-// back to back.  The producer never decodes, so consumers are never held back by a slow sibling: they
-// only ever wait for data.  Returns false if a stage never freed.
+// Producer warp.  What a block of steps needs (where each step reads and writes, which bytes to copy) is
+// worked out BEFORE the warp waits for the stage to come free: the path from "stage freed" to "bytes
+// landed" is what the decoding warps end up waiting for, and it then holds only the arming of the "full"
+// barrier, the stores of the offsets and the copies.  Lanes 0..kSS-1 issue one bulk copy each (the context
+// bytes of one step; two where a step starts in one row and ends in the next).  The producer never
+// decodes, so consumers are never held back by a slow sibling: they only ever wait for data.  Returns
+// false if a stage never freed.
 template <int SPAN, bool SPLIT>
 __device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uint32_t blk, uint32_t nblocks, int stall_block,
                                              uint32_t spin_limit) {
     constexpr uint32_t NST = ring_stages(SPAN);
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t spr = SPLIT ? 1u : it.col_len / it.k_eff;  // steps per row when rows hold whole steps
+    // row and column of the first element of this lane's step of the block, kept running instead of divided out
+    uint32_t run_r, run_c;
+    {
+        const unsigned long long e0 = (unsigned long long)lane * it.k_eff;
+        run_r = (uint32_t)(e0 / it.col_len);
+        run_c = (uint32_t)(e0 - (unsigned long long)run_r * it.col_len);
+    }
     for (uint32_t jb = 0; jb < nblocks; ++jb) {
         const uint32_t g = blk + jb, stage = g % NST, round = g / NST;
         const uint32_t full = smem_u32(&sm.full_bar[stage]);
         const uint32_t left = it.nsteps - jb * kSS;
         const uint32_t nst = left < (uint32_t)kSS ? left : (uint32_t)kSS;
-        int good = 1;
-        if (lane == 0) {
-            good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u, spin_limit) ? 1 : 0;
-            uint32_t bytes = nst * SPAN;
-            if (SPLIT && it.nsteps > it.nfull && jb * kSS + nst == it.nsteps) bytes -= SPAN - it.last_active;  // ragged last step
-            if (good) {
-                mbar_expect_tx(full, bytes);   // as early as possible: arming the barrier late costs the consumers dearly
-                sm.armed = g + 1;
-            }
-        }
-        good = __shfl_sync(0xFFFFFFFFu, good, 0);
-        if (!good) return false;
-        const bool stall = (int)g == stall_block;   // self-test: the bytes never come, the consumers' wait runs out
-        // where every step of the block reads and writes: the consumers take the offset from here
-        // instead of tracking rows themselves; every lane releases its offsets with its own arrive
-        const uint32_t dst = smem_u32(sm.ctxring) + (stage * kSS + lane) * SPAN;
-        if constexpr (!SPLIT) {
-            uint32_t ofs = 0;
-            if (lane < nst) {
+        uint32_t bytes = nst * SPAN;
+        if (SPLIT && it.nsteps > it.nfull && jb * kSS + nst == it.nsteps) bytes -= SPAN - it.last_active;  // ragged last step
+        // where this lane's step reads and writes: the consumers take the offset from shared memory instead
+        // of tracking rows themselves.  A step may start in one row and end in the next (never further: rows
+        // are at least as long as a step), so with SPLIT it is two copies and two offsets.
+        uint32_t ofs_a = 0, ofs_b = 0, part_a = 0, part_b = 0, split = 0;
+        if (lane < nst) {
+            const uint32_t rr = run_r, cc = run_c;
+            ofs_a = it.rowbase[rr < kRowCap ? rr : 0] + cc;
+            if constexpr (SPLIT) {
                 const uint32_t s = jb * kSS + lane;
-                const uint32_t rr = s / spr, cc = (s - rr * spr) * it.k_eff;
-                ofs = it.rowbase[rr < kRowCap ? rr : 0] + cc;
-                sm.stepofs[stage][lane] = ofs;
-            }
-            if (lane < (uint32_t)kSS) mbar_arrive(full);
-            if (lane < nst && !stall) bulk_g2s(dst, it.ctx_bytes + ofs + it.t_begin, SPAN, full);
-        } else {
-            // rows do not hold whole steps: a step may start in one row and end in the next (never further:
-            // rows are at least as long as a step), so it is two copies and two offsets
-            uint32_t ofs_a = 0, ofs_b = 0, part_a = 0, part_b = 0;
-            if (lane < nst) {
-                const uint32_t s = jb * kSS + lane;
-                const unsigned long long e0 = (unsigned long long)s * it.k_eff;
-                const uint32_t rr = (uint32_t)(e0 / it.col_len), cc = (uint32_t)(e0 - (unsigned long long)rr * it.col_len);
                 const uint32_t act = (s < it.nfull) ? SPAN : it.last_active;       // sub-streams with an element in this step
                 const uint32_t room = it.col_len - cc;                               // sub-streams 0..room-1 stay in row rr
-                const uint32_t split = room > it.t_begin ? (room - it.t_begin < SPAN ? room - it.t_begin : SPAN) : 0u;
-                ofs_a = it.rowbase[rr < kRowCap ? rr : 0] + cc;
+                split = room > it.t_begin ? (room - it.t_begin < SPAN ? room - it.t_begin : SPAN) : 0u;
                 ofs_b = it.rowbase[rr + 1 < kRowCap ? rr + 1 : 0] + cc - it.col_len;
                 part_a = split < act ? split : act;
                 part_b = act - part_a;
-                sm.stepofs[stage][lane] = ofs_a;
+            } else {
+                part_a = SPAN;
+            }
+        }
+        (void)spr;
+        const bool good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u, spin_limit);
+        if (!__all_sync(0xFFFFFFFFu, good)) return false;
+        if (lane == 0) {
+            mbar_expect_tx(full, bytes);   // as early as possible: arming the barrier late costs the consumers dearly
+            sm.armed = g + 1;
+        }
+        const bool stall = (int)g == stall_block;   // self-test: the bytes never come, the consumers' wait runs out
+        const uint32_t dst = smem_u32(sm.ctxring) + (stage * kSS + lane) * SPAN;
+        if (lane < nst) {
+            sm.stepofs[stage][lane] = ofs_a;
+            if constexpr (SPLIT) {
                 sm.stepofs_b[stage][lane] = ofs_b;
                 sm.stepsplit[stage][lane] = split;
             }
-            if (lane < (uint32_t)kSS) mbar_arrive(full);
-            if (part_a && !stall) bulk_g2s(dst, it.ctx_bytes + ofs_a + it.t_begin, part_a, full);
+        }
+        if (lane < (uint32_t)kSS) mbar_arrive(full);   // every lane releases its offsets with its own arrive
+        if (part_a && !stall) bulk_g2s(dst, it.ctx_bytes + ofs_a + it.t_begin, part_a, full);
+        if constexpr (SPLIT) {
             if (part_b && !stall) bulk_g2s(dst + part_a, it.ctx_bytes + ofs_b + it.t_begin + part_a, part_b, full);
         }
+        // the same lane's step of the next block lies kSS steps on
+        run_c += (uint32_t)kSS * it.k_eff;
+        while (run_c >= it.col_len) { run_c -= it.col_len; ++run_r; }
+    }
+    return true;
+}
+
+// Rows that do not hold whole steps, under an item that spans the bucket's sub-streams (SPAN == k_eff: the
+// down-projection shards of a tensor-parallel rank, 3584 columns under 1024 sub-streams).  A block of steps is
+// then one contiguous run of the bucket's elements, and so are its bytes in the ring: the block is copied as
+// one piece per row it touches (lane i: row of the block's first element + i) instead of one or two per step.
+// The offsets of every step are published as in producer_run<SPAN, true>, which the same loop reads.
+template <int SPAN>
+__device__ __forceinline__ bool producer_split_rows(Smem& sm, const StreamItem& it, uint32_t blk, uint32_t nblocks, int stall_block,
+                                                    uint32_t spin_limit) {
+    constexpr uint32_t NST = ring_stages(SPAN);
+    const uint32_t lane = threadIdx.x & 31u;
+    uint32_t br = 0, bc = 0;   // row and column of the block's first element
+    for (uint32_t jb = 0; jb < nblocks; ++jb) {
+        const uint32_t g = blk + jb, stage = g % NST, round = g / NST;
+        const uint32_t full = smem_u32(&sm.full_bar[stage]);
+        const uint32_t left = it.nsteps - jb * kSS;
+        const uint32_t nst = left < (uint32_t)kSS ? left : (uint32_t)kSS;
+        uint32_t bytes = nst * SPAN;
+        if (it.nsteps > it.nfull && jb * kSS + nst == it.nsteps) bytes -= SPAN - it.last_active;  // ragged last step
+        // this lane's step (lanes >= nst: unused): rows are longer than a step, so a few rounds at most
+        uint32_t rr = br, cc = bc + lane * SPAN;
+        while (cc >= it.col_len) { cc -= it.col_len; ++rr; }
+        const uint32_t room = it.col_len - cc;
+        const uint32_t split = room < SPAN ? room : SPAN;
+        const uint32_t ofs_a = it.rowbase[rr < kRowCap ? rr : 0] + cc;
+        const uint32_t ofs_b = it.rowbase[rr + 1 < kRowCap ? rr + 1 : 0] + cc - it.col_len;
+        // this lane's piece of the block: what the block holds of row br + lane
+        const uint32_t in_first = it.col_len - bc;
+        const uint32_t seg_off = lane == 0 ? 0u : in_first + (lane - 1u) * it.col_len;   // within the block
+        const uint32_t seg_cap = lane == 0 ? in_first : it.col_len;
+        const uint32_t seg_len = seg_off < bytes ? (bytes - seg_off < seg_cap ? bytes - seg_off : seg_cap) : 0u;
+        const uint32_t seg_row = br + lane;
+        const uint32_t seg_src = it.rowbase[seg_row < kRowCap ? seg_row : 0] + (lane == 0 ? bc : 0u);
+        const bool good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u, spin_limit);
+        if (!__all_sync(0xFFFFFFFFu, good)) return false;
+        if (lane == 0) {
+            mbar_expect_tx(full, bytes);
+            sm.armed = g + 1;
+        }
+        if (lane < nst) {
+            sm.stepofs[stage][lane] = ofs_a;
+            sm.stepofs_b[stage][lane] = ofs_b;
+            sm.stepsplit[stage][lane] = split;
+        }
+        if (lane < (uint32_t)kSS) mbar_arrive(full);
+        if (seg_len && (int)g != stall_block)
+            bulk_g2s(smem_u32(sm.ctxring) + stage * kSS * SPAN + seg_off, it.ctx_bytes + seg_src, seg_len, full);
+        bc += nst * SPAN;
+        while (bc >= it.col_len) { bc -= it.col_len; ++br; }
     }
     return true;
 }
@@ -667,6 +724,12 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
             __syncwarp();
             if ((tid & 31u) == 0) mbar_arrive(smem_u32(&sm.empty_bar[stage]) + dep);
         }
+        // (SPLIT) which of a step's two rows this thread's sub-streams lie in is settled here, so that the
+        // block below carries one offset per step like any other and not three
+        if constexpr (SPLIT) {
+#pragma unroll
+            for (int u = 0; u < kSS; ++u) ofs[u] = (tid * CH >= split[u]) ? ofs_b[u] : ofs[u];
+        }
         // a whole block runs without per-step checks; only the last block of an item can be shorter
         auto run_block = [&](auto checked) {
             constexpr bool CHECKED = decltype(checked)::value;
@@ -699,7 +762,6 @@ __device__ __forceinline__ bool stream_run(Smem& sm, const StreamItem& it, Strea
                         }
                     }
                     uint32_t o = ofs[u];
-                    if constexpr (SPLIT) o = (tid * CH >= split[u]) ? ofs_b[u] : o;
                     if constexpr (MROW) {
                         const uint32_t row = (jb * kSS + (uint32_t)u) * rows_step + my_row;
                         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(o) : "r"(rowbase_s + 4u * (row < (uint32_t)kRowCap ? row : 0u)) : "memory");
@@ -1246,6 +1308,7 @@ bucket_decode_kernel(const __grid_constant__ BatchArgs args, unsigned int* __res
                     }
                     if (fed) {
                     } else if (!split && it.k_eff == SPAN && (it.col_len & 15u) == 0u) run_ok = producer_rows<SPAN>(sm, it, blk, nblocks, stall_block, spin_limit);
+                    else if (split && it.k_eff == SPAN) run_ok = producer_split_rows<SPAN>(sm, it, blk, nblocks, stall_block, spin_limit);
                     else run_ok = split ? producer_run<SPAN, true>(sm, it, blk, nblocks, stall_block, spin_limit)
                                         : producer_run<SPAN, false>(sm, it, blk, nblocks, stall_block, spin_limit);
                 }
