@@ -551,21 +551,26 @@ __device__ __forceinline__ bool producer_mrow(Smem& sm, const StreamItem& it, ui
         const uint32_t full = smem_u32(&sm.full_bar[stage]);
         const uint32_t left = it.nsteps - jb * kSS;
         const uint32_t nst = left < (uint32_t)kSS ? left : (uint32_t)kSS;
-        int good = 1;
+        uint32_t bytes = nst * SPAN;
+        if (it.nsteps > it.nfull && jb * kSS + nst == it.nsteps) bytes -= SPAN - it.last_active;  // ragged last step: fewer rows
+        // this lane's first piece (its only one unless a block holds more than 32 rows of the item), worked
+        // out before the wait like everything else that does not need the stage
+        const uint32_t pieces = nst * rows_item;
+        const uint32_t u0 = lane / rows_item, j0 = lane - u0 * rows_item;
+        const uint32_t r0 = (jb * kSS + u0) * rows_step + row0 + j0;
+        const bool have0 = lane < pieces && r0 < it.nrows;
+        const uint32_t src0 = it.rowbase[r0 < kRowCap ? r0 : 0];
+        const bool good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u, spin_limit);
+        if (!__all_sync(0xFFFFFFFFu, good)) return false;
         if (lane == 0) {
-            good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u, spin_limit) ? 1 : 0;
-            uint32_t bytes = nst * SPAN;
-            if (it.nsteps > it.nfull && jb * kSS + nst == it.nsteps) bytes -= SPAN - it.last_active;  // ragged last step: fewer rows
-            if (good) {
-                mbar_expect_tx(full, bytes);
-                sm.armed = g + 1;
-            }
+            mbar_expect_tx(full, bytes);
+            sm.armed = g + 1;
         }
-        good = __shfl_sync(0xFFFFFFFFu, good, 0);
-        if (!good) return false;
         if (lane < (uint32_t)kSS) mbar_arrive(full);
         if ((int)g == stall_block) continue;   // self-test: the bytes never come, the consumers' wait runs out
-        for (uint32_t p = lane; p < nst * rows_item; p += 32u) {
+        if (have0)
+            bulk_g2s(smem_u32(sm.ctxring) + (stage * kSS + u0) * SPAN + j0 * it.col_len, it.ctx_bytes + src0, it.col_len, full);
+        for (uint32_t p = lane + 32u; p < pieces; p += 32u) {
             const uint32_t u = p / rows_item, j = p - u * rows_item;
             const uint32_t row = (jb * kSS + u) * rows_step + row0 + j;
             if (row < it.nrows)
