@@ -18,9 +18,11 @@
 //    bulk-copied raw into the table's own space and expanded in place;
 //  * each thread decodes CH adjacent sub-streams in lock-step: CH independent dependency chains for
 //    ILP, one CH-byte context read and one 2*CH-byte BF16 store per step, both fully coalesced across
-//    the warp; context bytes arrive through cp.async.bulk issued by a producer warp, the bitstream
-//    through a ring of 16-byte cp.async chunks per sub-stream, or whole with one bulk copy when the
-//    bucket's code bits fit the rings' space;
+//    the warp; context bytes arrive through cp.async.bulk issued by a producer warp (a block of eight
+//    steps at a time, one copy per row the block touches, everything worked out before the warp waits
+//    for the block's stage to come free: the three-stage ring runs close to dry), the bitstream through
+//    a ring of 16-byte cp.async chunks per sub-stream, or whole with one bulk copy when the bucket's code
+//    bits fit the rings' space;
 //  * every sub-stream decodes from a 32-bit left-aligned window that is rebuilt from its bit position
 //    every (32 - L) / L + 1 symbols, branch-free, so that the rebuild is warp-uniform;
 //  * ESC (raw 16-bit symbol after the code) is rare: buckets whose tables contain no ESC entry run
@@ -412,12 +414,14 @@ __device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uin
         (void)spr;
         const bool good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u, spin_limit);
         if (!__all_sync(0xFFFFFFFFu, good)) return false;
-        if (lane == 0) {
-            mbar_expect_tx(full, bytes);   // as early as possible: arming the barrier late costs the consumers dearly
-            sm.armed = g + 1;
-        }
+        if (lane == 0) mbar_expect_tx(full, bytes);   // as early as possible: arming the barrier late costs the consumers dearly
         const bool stall = (int)g == stall_block;   // self-test: the bytes never come, the consumers' wait runs out
         const uint32_t dst = smem_u32(sm.ctxring) + (stage * kSS + lane) * SPAN;
+        if (part_a && !stall) bulk_g2s(dst, it.ctx_bytes + ofs_a + it.t_begin, part_a, full);
+        if constexpr (SPLIT) {
+            if (part_b && !stall) bulk_g2s(dst + part_a, it.ctx_bytes + ofs_b + it.t_begin + part_a, part_b, full);
+        }
+        if (lane == 0) sm.armed = g + 1;
         if (lane < nst) {
             sm.stepofs[stage][lane] = ofs_a;
             if constexpr (SPLIT) {
@@ -426,10 +430,6 @@ __device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uin
             }
         }
         if (lane < (uint32_t)kSS) mbar_arrive(full);   // every lane releases its offsets with its own arrive
-        if (part_a && !stall) bulk_g2s(dst, it.ctx_bytes + ofs_a + it.t_begin, part_a, full);
-        if constexpr (SPLIT) {
-            if (part_b && !stall) bulk_g2s(dst + part_a, it.ctx_bytes + ofs_b + it.t_begin + part_a, part_b, full);
-        }
         // the same lane's step of the next block lies kSS steps on
         run_c += (uint32_t)kSS * it.k_eff;
         while (run_c >= it.col_len) { run_c -= it.col_len; ++run_r; }
@@ -471,18 +471,16 @@ __device__ __forceinline__ bool producer_split_rows(Smem& sm, const StreamItem& 
         const uint32_t seg_src = it.rowbase[seg_row < kRowCap ? seg_row : 0] + (lane == 0 ? bc : 0u);
         const bool good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u, spin_limit);
         if (!__all_sync(0xFFFFFFFFu, good)) return false;
-        if (lane == 0) {
-            mbar_expect_tx(full, bytes);
-            sm.armed = g + 1;
-        }
+        if (lane == 0) mbar_expect_tx(full, bytes);
+        if (seg_len && (int)g != stall_block)
+            bulk_g2s(smem_u32(sm.ctxring) + stage * kSS * SPAN + seg_off, it.ctx_bytes + seg_src, seg_len, full);
+        if (lane == 0) sm.armed = g + 1;
         if (lane < nst) {
             sm.stepofs[stage][lane] = ofs_a;
             sm.stepofs_b[stage][lane] = ofs_b;
             sm.stepsplit[stage][lane] = split;
         }
         if (lane < (uint32_t)kSS) mbar_arrive(full);
-        if (seg_len && (int)g != stall_block)
-            bulk_g2s(smem_u32(sm.ctxring) + stage * kSS * SPAN + seg_off, it.ctx_bytes + seg_src, seg_len, full);
         bc += nst * SPAN;
         while (bc >= it.col_len) { bc -= it.col_len; ++br; }
     }
@@ -521,14 +519,13 @@ __device__ __forceinline__ bool producer_rows(Smem& sm, const StreamItem& it, ui
         const uint32_t seg_src = it.rowbase[seg_row < kRowCap ? seg_row : 0] + (lane == 0 ? sc * SPAN : 0u);
         const bool good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u, spin_limit);
         if (!__all_sync(0xFFFFFFFFu, good)) return false;
-        if (lane == 0) {
-            mbar_expect_tx(full, nst * SPAN);         // as early as possible: arming the barrier late costs the consumers dearly
-            sm.armed = g + 1;
-        }
-        if (lane < nst) sm.stepofs[stage][lane] = ofs;
-        if (lane < (uint32_t)kSS) mbar_arrive(full);  // every lane releases its offset with its own arrive
+        // arm, copy, and only then publish the offsets: the bytes have the longest way to go
+        if (lane == 0) mbar_expect_tx(full, nst * SPAN);
         // (self-test: the bytes of one block never come, the consumers' wait runs out)
         if (seg_n && (int)g != stall_block) bulk_g2s(smem_u32(sm.ctxring) + (stage * kSS + seg_s0) * SPAN, src0 + seg_src, seg_n * SPAN, full);
+        if (lane == 0) sm.armed = g + 1;
+        if (lane < nst) sm.stepofs[stage][lane] = ofs;
+        if (lane < (uint32_t)kSS) mbar_arrive(full);  // every lane releases its offset with its own arrive
         sc += nst;
         while (sc >= spr) { sc -= spr; ++rr; }
     }

@@ -80,6 +80,14 @@ def test_tp8_shard_shapes(dev, name, n, m):
     _fp8_roundtrip(n, m, "normal", "channel", 500 + n % 97, dev, with_oracle=n * m <= 1024 * 8192)
 
 
+@pytest.mark.parametrize("n,m", [(5, 3584), (3, 1552), (7, 2064), (130, 1040), (64, 3600)], ids=lambda v: str(v))
+def test_rows_that_split_steps_with_a_ragged_last_step(dev, n, m):
+    """Rows longer than a step that do not hold whole steps (widths that are multiples of 16 but not of
+    1024), in buckets whose element count is no multiple of the sub-streams either: the last step holds an
+    element for the first sub-streams only.  One scale for the whole tensor, so a bucket is up to 128 rows."""
+    _fp8_roundtrip(n, m, "normal", "tensor", 77 + n, dev, with_oracle=True)
+
+
 def test_tp8_shards_in_one_plan(dev):
     """All seven shards of one layer of a TP=8 rank through one persistent launch."""
     import MPServe_cuda
