@@ -28,8 +28,9 @@ __all__ = [
 
 # Sub-streams per bucket: the reference builds and decodes at most 1024 (one thread of one block each,
 # kernel/build_huffman.cu:313, kernel/decode_huffman.cu:695); this library up to MAX_SUBSTREAMS
-# (include/mpserve_b200.h).  The decode calls below accept both; the builders under the reference's names
-# keep the reference's limit, build_fp8_fine_substreams is the way to more.
+# (include/mpserve_b200.h).  The decode calls for rectangular buckets (FP8, AWQ) accept both, the by-scale
+# call keeps the reference's limit (no builder here writes more); the builders under the reference's
+# names keep the reference's limit too, build_fp8_fine_substreams is the way to more.
 MAX_SUBSTREAMS_REFERENCE = 1024
 MAX_SUBSTREAMS = 8192
 
