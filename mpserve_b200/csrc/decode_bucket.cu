@@ -1570,9 +1570,11 @@ static int validate_tensor(const mps_bucket_tensor& T, int L) {
 }
 
 // Tensors whose sub-streams hold this few symbols (on average) are decoded by the direct kernel.  It
-// pays about ten times more per symbol of a sub-stream than the persistent kernel, whose fixed cost
-// per bucket is worth about ten such symbols: that is the break-even.
-constexpr long long kDirectMaxSteps = 8;
+// pays about ten times more per symbol of a sub-stream than the persistent kernel, whose cost before a
+// bucket's first symbol is worth some twenty such symbols.  Measured on single per-channel tensors of
+// 67 to 291 buckets: 0.4-0.9 K elements per bucket 11-13 us direct against 16-20 us persistent, 1.8-2.6 K
+// a tie, 6.6 K 30 against 21 us, 8.7 K 42 against 23 us.
+constexpr long long kDirectMaxSteps = 2;
 
 static bool use_direct(const mps_bucket_tensor& T) {
     const int forced = env_int("MPS_DECODE_DIRECT", -1);
