@@ -456,7 +456,7 @@ __device__ __forceinline__ bool producer_split_rows(Smem& sm, const StreamItem& 
         uint32_t bytes = nst * SPAN;
         if (it.nsteps > it.nfull && jb * kSS + nst == it.nsteps) bytes -= SPAN - it.last_active;  // ragged last step
         // this lane's step (lanes >= nst: unused): rows are longer than a step, so a few rounds at most
-        uint32_t rr = br, cc = bc + lane * SPAN;
+        uint32_t rr = br, cc = bc + (lane < (uint32_t)kSS ? lane : 0u) * SPAN;
         while (cc >= it.col_len) { cc -= it.col_len; ++rr; }
         const uint32_t room = it.col_len - cc;
         const uint32_t split = room < SPAN ? room : SPAN;
@@ -507,7 +507,10 @@ __device__ __forceinline__ bool producer_rows(Smem& sm, const StreamItem& it, ui
         const uint32_t left = it.nsteps - jb * kSS;
         const uint32_t nst = left < (uint32_t)kSS ? left : (uint32_t)kSS;
         // this lane's step (lanes >= nst: unused) ...
-        uint32_t my_r = rr, my_s = sc + lane;
+        // (no loop over lanes' worth of rows where a row is one step: this runs once per block, and when the
+        // stage is already free it is time the decoding warps wait)
+        uint32_t my_r = rr, my_s = sc + (lane < (uint32_t)kSS ? lane : 0u);
+        if (spr == 1u) { my_r += my_s; my_s = 0u; }
         while (my_s >= spr) { my_s -= spr; ++my_r; }
         const uint32_t ofs = it.rowbase[my_r < kRowCap ? my_r : 0] + my_s * SPAN;
         // ... and this lane's piece of the block: lane i copies what the block takes of row rr + i
@@ -527,6 +530,7 @@ __device__ __forceinline__ bool producer_rows(Smem& sm, const StreamItem& it, ui
         if (lane < nst) sm.stepofs[stage][lane] = ofs;
         if (lane < (uint32_t)kSS) mbar_arrive(full);  // every lane releases its offset with its own arrive
         sc += nst;
+        if (spr == 1u) { rr += sc; sc = 0u; }
         while (sc >= spr) { sc -= spr; ++rr; }
     }
     return true;
