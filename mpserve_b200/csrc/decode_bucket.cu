@@ -1810,7 +1810,7 @@ int mps_bucket_batch_plan(const mps_bucket_tensor* tensors_host, int count, int6
     }
     const int L = (tensors_host[0].mode == 0) ? 7 : 11;
     long long subs = 0;
-    int k_min = 1024;
+    int k_min = MPS_MAX_SUBSTREAMS;
     for (int i = 0; i < count; ++i) {
         int rc = validate_tensor(tensors_host[i], L);
         if (rc) return rc;
