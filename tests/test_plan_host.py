@@ -84,3 +84,19 @@ def test_null_pointer_and_mode_mismatch_are_refused():
     assert _plan([t])[0] == _lib.MPS_ERR_INVALID
     by_scale = _tensor(4096, 4096, 462, 256, mode=2, group_size=0)      # by-scale groups need their size
     assert _plan([by_scale])[0] == _lib.MPS_ERR_INVALID
+
+
+def test_decode_argument_check_takes_finer_sub_streams():
+    """The Python-side check of the rectangular decode calls: up to MAX_SUBSTREAMS sub-streams per bucket."""
+    import torch
+
+    from mpserve_b200 import api
+
+    B = 3
+    i32 = lambda n: torch.zeros(n, dtype=torch.int32)
+    args = lambda k: (i32(B), i32(B), i32(B + 1), i32(7), torch.zeros((B, k + 1), dtype=torch.uint32),
+                      torch.zeros(B + 1, dtype=torch.int64), B)
+    assert api._check_rect(*args(1024)) == 1024
+    assert api._check_rect(*args(api.MAX_SUBSTREAMS)) == api.MAX_SUBSTREAMS
+    with pytest.raises(ValueError, match="invalid k"):
+        api._check_rect(*args(api.MAX_SUBSTREAMS + 1))
