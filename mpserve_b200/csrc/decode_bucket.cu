@@ -377,7 +377,6 @@ __device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uin
                                              uint32_t spin_limit) {
     constexpr uint32_t NST = ring_stages(SPAN);
     const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t spr = SPLIT ? 1u : it.col_len / it.k_eff;  // steps per row when rows hold whole steps
     // row and column of the first element of this lane's step of the block, kept running instead of divided out
     uint32_t run_r, run_c;
     {
@@ -411,7 +410,6 @@ __device__ __forceinline__ bool producer_run(Smem& sm, const StreamItem& it, uin
                 part_a = SPAN;
             }
         }
-        (void)spr;
         const bool good = mbar_wait(smem_u32(&sm.empty_bar[stage]), (round & 1u) ^ 1u, spin_limit);
         if (!__all_sync(0xFFFFFFFFu, good)) return false;
         if (lane == 0) mbar_expect_tx(full, bytes);   // as early as possible: arming the barrier late costs the consumers dearly
