@@ -100,3 +100,26 @@ def test_decode_argument_check_takes_finer_sub_streams():
     assert api._check_rect(*args(api.MAX_SUBSTREAMS)) == api.MAX_SUBSTREAMS
     with pytest.raises(ValueError, match="invalid k"):
         api._check_rect(*args(api.MAX_SUBSTREAMS + 1))
+
+
+@pytest.mark.parametrize("n,m,k", [(64, 512, 2048), (9, 1000, 4096), (3, 5, 8192)])
+def test_oracle_round_trip_with_the_limit_lifted(n, m, k):
+    """The checker of the finer sub-streams: the oracle's layout code takes any sub-stream count once its
+    argument check (the reference's, 1024) is lifted, and its decode restores the source."""
+    import numpy as np
+    import torch
+
+    from mpserve_b200 import workloads as wl
+    from oracle import oracle as orc
+
+    c = wl.quantize_fp8(wl.random_weight(n, m, 5 + n, "normal"), "channel")
+    bits = c.bf16.view(torch.uint16).numpy()
+    with pytest.raises(ValueError, match="1024"):
+        orc.build_fp8(bits, c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, k)
+    orc.set_substream_limit(8192)
+    try:
+        art = orc.build_fp8(bits, c.fp8_u8.numpy(), c.scales_u16.numpy(), 7, k)
+    finally:
+        orc.set_substream_limit(1024)
+    assert art["bucket_thread_startbit_u32"].shape[1] == k + 1
+    np.testing.assert_array_equal(orc.decode_fp8(c.fp8_u8.numpy(), art, n, m), bits)
